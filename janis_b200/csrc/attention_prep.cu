@@ -1,0 +1,282 @@
+// What stands between an attention's projections and its scores, for mixers that filter, norm or compress their
+// queries, keys and values before they cache them, and small products that run head by head.
+//
+//   qkv_conv_norm_store   a short causal filter over time on every channel of q | k | v (taps that reach back before
+//                         the step come from the slot's kept inputs), an RMS norm over the whole of q and over the
+//                         whole of k (one mean over all heads, a weight vector each), every value head divided by its
+//                         own root mean square, q written to rows of its own, k and v into the paged cache line.
+//                         Each of the steps is optional.
+//   latent_rotate_store   a compressed key/value row [c | r]: c RMS-normed with a weight, r turned by the token's
+//                         position (neighbouring pairs 2i, 2i + 1 of its first `rot` features; sine and cosine times an amplitude), the two written
+//                         side by side as the one "key" of a cache line with a single head; the turned part of every
+//                         query head is turned the same way and written behind the place of its absorbed part.
+//   head_linear           out[t, h, :] = W[h] x[t, h, :] for every head h: a product per head with its own matrix.
+//
+// All sums, roots and angles are float whatever is stored.  A sum's order depends on the sizes alone.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace janis {
+
+constexpr int PREP_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_THREADS)
+qkv_conv_norm_store_kernel(const T* __restrict__ rows, int row_elems, int H, int G, int d, int dv, int K,
+                           const float* __restrict__ conv_w, float* __restrict__ conv_state,
+                           const float* __restrict__ wq, const float* __restrict__ wk, int v_unit, float eps,
+                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                           const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                           const int* __restrict__ seq_start, const int* __restrict__ seq_end, T* __restrict__ q_out,
+                           T* __restrict__ kpool, T* __restrict__ vpool, const int* __restrict__ page_table,
+                           int table_stride) {
+    extern __shared__ float prep_smem[];
+    const int Cq = H * d, Ck = G * d, Cv = G * dv, C = Cq + Ck + Cv;
+    float* x_s = prep_smem;                 // the token's filtered row
+    float* inv_s = x_s + C;                 // 1 / rms of q, of k, of each value head
+    float* scratch = inv_s + 2 + G;         // 32 floats for block sums
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = PREP_THREADS >> 5;
+    grid_dependents_launch();
+    const int s = tok_seq[t], slot = seq_slot[s], pos = tok_pos[t], i = t - seq_first_row[s];
+    const bool alone = seq_end[s] - seq_start[s] == 1;      // the sequence's only token of the step shifts the kept inputs itself
+    grid_dependency_wait();
+    const T* row = rows + (size_t)t * row_elems;
+    if (conv_w != nullptr && K > 1) {
+        float* st = slot >= 0 ? conv_state + (size_t)slot * (K - 1) * C : nullptr;
+        for (int c = tid; c < C; c += PREP_THREADS) {
+            float acc = 0.f, xs[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j >= K) break;
+                const int idx = i - j;                      // the input j tokens back
+                float x = 0.f;
+                if (idx >= 0) x = to_float(rows[(size_t)(t - j) * row_elems + c]);
+                else if (st != nullptr) x = st[(size_t)(K - 1 + idx) * C + c];
+                xs[j] = x;
+                acc = fmaf(conv_w[(size_t)c * K + K - 1 - j], x, acc);
+            }
+            x_s[c] = acc;
+            if (alone && st != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 15; ++j) {
+                    if (j >= K - 1) break;
+                    st[(size_t)(K - 2 - j) * C + c] = xs[j];
+                }
+            }
+        }
+    } else {
+        const float w0 = conv_w != nullptr ? 1.f : 0.f;     // (a filter of one tap scales the channel)
+        for (int c = tid; c < C; c += PREP_THREADS) {
+            const float x = to_float(row[c]);
+            x_s[c] = w0 != 0.f ? x * conv_w[c] : x;
+        }
+    }
+    __syncthreads();
+    {
+        float sq = 0.f, sk = 0.f;
+        if (wq != nullptr)
+            for (int c = tid; c < Cq; c += PREP_THREADS) sq = fmaf(x_s[c], x_s[c], sq);
+        if (wk != nullptr)
+            for (int c = tid; c < Ck; c += PREP_THREADS) sk = fmaf(x_s[Cq + c], x_s[Cq + c], sk);
+        sq = block_sum(sq, scratch);
+        sk = block_sum(sk, scratch);
+        if (tid == 0) {
+            inv_s[0] = wq != nullptr ? 1.f / sqrtf(sq / (float)Cq + eps) : 1.f;
+            inv_s[1] = wk != nullptr ? 1.f / sqrtf(sk / (float)Ck + eps) : 1.f;
+        }
+        for (int g = warp; g < G; g += nwarp) {
+            float sv = 0.f;
+            if (v_unit)
+                for (int c = lane; c < dv; c += 32) {
+                    const float v = x_s[Cq + Ck + g * dv + c];
+                    sv = fmaf(v, v, sv);
+                }
+            sv = warp_sum(sv);
+            if (lane == 0) inv_s[2 + g] = v_unit ? 1.f / sqrtf(sv / (float)dv + eps) : 1.f;
+        }
+    }
+    __syncthreads();
+    T* q_row = q_out + (size_t)t * Cq;
+    const float iq = inv_s[0], ik = inv_s[1];
+    for (int c = tid; c < Cq; c += PREP_THREADS) q_row[c] = from_float<T>(wq != nullptr ? x_s[c] * iq * wq[c] : x_s[c]);
+    if (slot < 0) return;                                   // a padding row: its keys and values are stored nowhere
+    const int page = page_table[(size_t)slot * table_stride + pos / JANIS_PAGE];
+    T* kdst = kpool + ((size_t)page * G * JANIS_PAGE + pos % JANIS_PAGE) * d;
+    T* vdst = vpool + ((size_t)page * G * JANIS_PAGE + pos % JANIS_PAGE) * dv;
+    for (int c = tid; c < Ck; c += PREP_THREADS) {
+        const float v = wk != nullptr ? x_s[Cq + c] * ik * wk[c] : x_s[Cq + c];
+        kdst[(size_t)(c / d) * JANIS_PAGE * d + c % d] = from_float<T>(v);
+    }
+    for (int c = tid; c < Cv; c += PREP_THREADS) {
+        const int g = c / dv;
+        vdst[(size_t)g * JANIS_PAGE * dv + c % dv] = from_float<T>(x_s[Cq + Ck + c] * inv_s[2 + g]);
+    }
+}
+
+// rows[t]: q (H heads of d + dr) at 0, then at lat_off the compressed row [c (R) | r (dr)].
+// qfull[t, h, R : R + dr] = turn(q[t, h, d : d + dr]); the line's key at the token's position = [norm(c) | turn(r)].
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_rotate_store_kernel(const T* __restrict__ rows, int row_elems, int lat_off, int H, int d, int dr, int rot, int R,
+                           const float* __restrict__ wc, float eps, const float* __restrict__ inv_freq, float amp,
+                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                           const int* __restrict__ seq_slot, T* __restrict__ qfull, T* __restrict__ kpool,
+                           const int* __restrict__ page_table, int table_stride) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    grid_dependents_launch();
+    const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
+    T* kdst = nullptr;
+    if (slot >= 0) {
+        const int page = page_table[(size_t)slot * table_stride + pos / JANIS_PAGE];
+        kdst = kpool + ((size_t)page * JANIS_PAGE + pos % JANIS_PAGE) * (R + dr);
+    }
+    grid_dependency_wait();
+    const T* row = rows + (size_t)t * row_elems;
+    const T* lat = row + lat_off;
+    float ss = 0.f;
+    for (int c = tid; c < R; c += nt) {
+        const float v = to_float(lat[c]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)R + eps);
+    if (kdst != nullptr)
+        for (int c = tid; c < R; c += nt) kdst[c] = from_float<T>(to_float(lat[c]) * inv * wc[c]);
+    const int hr = dr >> 1, D = R + dr;
+    // unit 0 is the shared key part, units 1 .. H the query heads
+    for (int u = tid; u < (H + 1) * hr; u += nt) {
+        const int unit = u / hr, p = u % hr;
+        float sn = 0.f, cs = 1.f;                             // pairs from rot / 2 on pass as they are
+        if (2 * p < rot) {
+            sincosf((float)pos * inv_freq[p], &sn, &cs);
+            sn *= amp;
+            cs *= amp;
+        }
+        const T* src = unit == 0 ? lat + R : row + (size_t)(unit - 1) * (d + dr) + d;
+        const float a = to_float(src[2 * p]), b = to_float(src[2 * p + 1]);
+        const float lo = a * cs - b * sn, hi = b * cs + a * sn;
+        if (unit == 0) {
+            if (kdst != nullptr) {
+                kdst[R + 2 * p] = from_float<T>(lo);
+                kdst[R + 2 * p + 1] = from_float<T>(hi);
+            }
+        } else {
+            T* dst = qfull + ((size_t)t * H + (unit - 1)) * D + R;
+            dst[2 * p] = from_float<T>(lo);
+            dst[2 * p + 1] = from_float<T>(hi);
+        }
+    }
+}
+
+// out[t, h * o_head + o_off + o] = sum_i W[h, o, i] x[t, h * x_head + x_off + i]; a CTA takes 8 tokens of one head and 8
+// outputs, a warp an output: lanes stride over i, then a butterfly.
+constexpr int HL_TOK = 8, HL_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(HL_WARPS * 32)
+head_linear_kernel(const T* __restrict__ x, int x_stride, int x_head, int x_off, const T* __restrict__ w,
+                   T* __restrict__ out, int o_stride, int o_head, int o_off, int n_tok, int I, int O) {
+    extern __shared__ float hl_smem[];
+    const int t0 = blockIdx.x * HL_TOK, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_here = min(HL_TOK, n_tok - t0);
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (int u = tid; u < HL_TOK * I; u += HL_WARPS * 32) {
+        const int tt = u / I, i = u % I;
+        hl_smem[u] = tt < n_here ? to_float(x[(size_t)(t0 + tt) * x_stride + (size_t)h * x_head + x_off + i]) : 0.f;
+    }
+    __syncthreads();
+    for (int o = blockIdx.z * HL_WARPS + warp; o < O; o += gridDim.z * HL_WARPS) {
+        const T* wr = w + ((size_t)h * O + o) * I;
+        float acc[HL_TOK];
+#pragma unroll
+        for (int tt = 0; tt < HL_TOK; ++tt) acc[tt] = 0.f;
+        for (int i = lane; i < I; i += 32) {
+            const float wv = to_float(wr[i]);
+#pragma unroll
+            for (int tt = 0; tt < HL_TOK; ++tt) acc[tt] = fmaf(wv, hl_smem[tt * I + i], acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < HL_TOK; ++tt) {
+            const float v = warp_sum(acc[tt]);
+            if (lane == 0 && tt < n_here)
+                out[(size_t)(t0 + tt) * o_stride + (size_t)h * o_head + o_off + o] = from_float<T>(v);
+        }
+    }
+}
+
+}  // namespace janis
+
+using namespace janis;
+
+JANIS_EXPORT int janis_qkv_conv_norm_store(const void* rows, int dtype, int row_elems, int T, int H, int G, int d, int dv,
+                                           int K, const float* conv_w, float* conv_state, const float* wq,
+                                           const float* wk, int v_unit, float eps, const int* tok_pos,
+                                           const int* tok_seq, const int* seq_slot, const int* seq_first_row,
+                                           const int* seq_start, const int* seq_end, void* q_out, void* kpool,
+                                           void* vpool, const int* page_table, int table_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long long C = (long long)H * d + (long long)G * (d + dv);
+    if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || row_elems < C) return fail("qkv_conv_norm_store: rows of %d elements do not hold %d + %d heads", row_elems, H, G);
+    if (conv_w != nullptr && (K < 1 || K > 16)) return fail("qkv_conv_norm_store: %d taps (1 to 16 are taken)", K);
+    if (conv_w != nullptr && K > 1 && conv_state == nullptr) return fail("qkv_conv_norm_store: a filter needs its kept inputs");
+    const size_t bytes = ((size_t)C + 2 + G + 32) * sizeof(float);
+    if (bytes > 200 * 1024) return fail("qkv_conv_norm_store: a row of %lld channels does not fit shared memory", C);
+#define JANIS_PREP_LAUNCH(TT)                                                                                          \
+    {                                                                                                                  \
+        static size_t most = 0;                                                                                        \
+        if (bytes > most && bytes > 48 * 1024) {                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(qkv_conv_norm_store_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
+            if (e != cudaSuccess) return fail("qkv_conv_norm_store: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e)); \
+            most = bytes;                                                                                              \
+        }                                                                                                              \
+        return launch_kernel("qkv_conv_norm_store", qkv_conv_norm_store_kernel<TT>, dim3(T), dim3(PREP_THREADS), bytes, \
+                             stream, 1, (const TT*)rows, row_elems, H, G, d, dv, K, conv_w, conv_state, wq, wk, v_unit, \
+                             eps, tok_pos, tok_seq, seq_slot, seq_first_row, seq_start, seq_end, (TT*)q_out, (TT*)kpool, \
+                             (TT*)vpool, page_table, table_stride);                                                    \
+    }
+    if (dtype == JANIS_F32) JANIS_PREP_LAUNCH(float)
+    if (dtype == JANIS_BF16) JANIS_PREP_LAUNCH(bf16)
+#undef JANIS_PREP_LAUNCH
+    return fail("qkv_conv_norm_store: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_latent_rotate_store(const void* rows, int dtype, int row_elems, int lat_off, int T, int H, int d,
+                                           int dr, int rot, int R, const float* wc, float eps, const float* inv_freq, float amp,
+                                           const int* tok_pos, const int* tok_seq, const int* seq_slot, void* qfull,
+                                           void* kpool, const int* page_table, int table_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || d < 0 || dr < 0 || (dr & 1) || R <= 0) return fail("latent_rotate_store: sizes %d heads, %d + %d, rank %d", H, d, dr, R);
+    if (rot < 0 || (rot & 1) || rot > dr) return fail("latent_rotate_store: %d of %d features turned", rot, dr);
+    if (lat_off < H * (d + dr) || lat_off + R + dr > row_elems) return fail("latent_rotate_store: rows of %d elements are too short", row_elems);
+    if (dtype == JANIS_F32)
+        return launch_kernel("latent_rotate_store", latent_rotate_store_kernel<float>, dim3(T), dim3(128), 0, stream, 1,
+                             (const float*)rows, row_elems, lat_off, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
+                             seq_slot, (float*)qfull, (float*)kpool, page_table, table_stride);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("latent_rotate_store", latent_rotate_store_kernel<bf16>, dim3(T), dim3(128), 0, stream, 1,
+                             (const bf16*)rows, row_elems, lat_off, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
+                             seq_slot, (bf16*)qfull, (bf16*)kpool, page_table, table_stride);
+    return fail("latent_rotate_store: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_head_linear(const void* x, int dtype, int x_stride, int x_head, int x_off, const void* w, void* out,
+                                   int o_stride, int o_head, int o_off, int T, int H, int I, int O, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || I <= 0 || O <= 0) return fail("head_linear: %d heads, %d -> %d", H, I, O);
+    const size_t bytes = (size_t)HL_TOK * I * sizeof(float);
+    if (bytes > 48 * 1024) return fail("head_linear: heads of %d inputs do not fit shared memory", I);
+    int gz = (O + HL_WARPS - 1) / HL_WARPS;
+    if (gz > 65535) gz = 65535;
+    if (H > 65535) return fail("head_linear: too many heads (%d)", H);
+    const dim3 grid((T + HL_TOK - 1) / HL_TOK, H, gz), block(HL_WARPS * 32);
+    if (dtype == JANIS_F32)
+        return launch_kernel("head_linear", head_linear_kernel<float>, grid, block, bytes, stream, 1, (const float*)x, x_stride,
+                             x_head, x_off, (const float*)w, (float*)out, o_stride, o_head, o_off, T, I, O);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("head_linear", head_linear_kernel<bf16>, grid, block, bytes, stream, 1, (const bf16*)x, x_stride,
+                             x_head, x_off, (const bf16*)w, (bf16*)out, o_stride, o_head, o_off, T, I, O);
+    return fail("head_linear: unknown dtype %d", dtype);
+}

@@ -1,4 +1,4 @@
-// Attention whose heads talk to each other before the softmax, over the paged cache.
+// Attention whose heads talk to each other, before the softmax or after it, over the paged cache.
 //
 //   raw_g[i, j]   = (q_g[i] . k_kv(g)[j]) * scale            for every query head g
 //   s_h[i, j]     = sum_g M[h, g] raw_g[i, j]                (M: heads x heads, optional)
@@ -9,6 +9,13 @@
 // floor(i / B), and, with a window W > 0, i - j < W.  sink is 1 (a key of score 0 without a value) or 0.  Keys have `d` features and values `dv`,
 // which need not be equal.  Values may be stored rotated by their own position (pairs m, m + dv/2, angle
 // j * inv_v[m]); the head's output is then turned back by the query's position.
+//
+// Options: a cap on the scaled scores, raw <- cap tanh(raw / cap), before anything else; a learnt sink per head
+// (sink_vals: exp(sink_h) joins the denominator instead of 1); values that are the first dv features of the cached
+// keys (v_stride = d: a line that keeps one vector per position for both); and the heads mixed *after* the
+// softmax, p'_h = sum_g M[h, g] softmax(raw_g), which takes two passes over the keys: the first leaves every
+// (row, head)'s maximum and denominator (`stats`), the second forms the final weights of all heads for a tile of
+// keys, mixes them and adds the values up; nothing is rescaled in it.
 //
 // Every kernel here reads keys and values from the cache line only, so a step stores first and attends
 // afterwards, and a prompt that continues, a decode step and a layer that reads another layer's line are the
@@ -108,11 +115,15 @@ struct TalkShape {
     int window;         // keys are seen among the query's last `window` positions (0: no such limit)
     int kt;             // keys per tile (<= 32)
     float scale;
+    float cap;          // > 0: raw <- cap tanh(raw / cap)
+    int mode;           // 0: one pass (heads mixed before the softmax, if at all); 1: maxima and denominators only, into
+                        // `stats`; 2: the weights from `stats`, mixed over the heads after the softmax, times the values
+    int v_stride;       // elements between the value rows of neighbouring positions (dv; d when values live in the keys)
 };
 
 __host__ __device__ inline size_t talk_plain_smem_floats(int H, int G, int d, int dv, int kt) {
     return (size_t)H * d + (size_t)H * H + (size_t)kt * (G * d + 1) + (size_t)kt * G * dv + 2 * (size_t)H * kt +
-           (size_t)H * dv + 3 * (size_t)H;
+           (size_t)H * dv + 5 * (size_t)H;
 }
 
 template <typename T>
@@ -121,7 +132,8 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
                             const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                             const T* __restrict__ kpool, const T* __restrict__ vpool,
                             const int* __restrict__ page_table, int table_stride, const float* __restrict__ talk,
-                            const float* __restrict__ inv_v, T* __restrict__ out, TalkShape sh) {
+                            const float* __restrict__ inv_v, T* __restrict__ out, const float* __restrict__ sink_vals,
+                            float* __restrict__ stats, TalkShape sh) {
     extern __shared__ float smem[];
     const int H = sh.H, G = sh.G, d = sh.d, dv = sh.dv, KT = sh.kt, rep = H / G;
     const int kstride = G * d + 1;
@@ -135,6 +147,8 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
     float* m_s = o_s + (size_t)H * dv;
     float* l_s = m_s + H;
     float* corr_s = l_s + H;
+    float* fm_s = corr_s + H;                         // mode 2: every head's final maximum and 1 / denominator
+    float* fl_s = fm_s + H;
     const int t = blockIdx.x, tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = nt >> 5;
     grid_dependents_launch();
     const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
@@ -143,6 +157,10 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
     grid_dependency_wait();
     T* o_row = out + (size_t)t * H * dv;
     if (slot < 0) {                                   // a padding row: written, never read
+        if (sh.mode == 1) {
+            for (int u = tid; u < 2 * H; u += nt) stats[(size_t)t * 2 * H + u] = 0.f;
+            return;
+        }
         for (int u = tid; u < H * dv; u += nt) o_row[u] = from_float<T>(0.f);
         return;
     }
@@ -150,8 +168,15 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
     for (int u = tid; u < H * d; u += nt) q_s[u] = to_float(q[u]);
     for (int u = tid; u < H * dv; u += nt) o_s[u] = 0.f;
     for (int u = tid; u < H; u += nt) {
-        m_s[u] = sh.sink ? 0.f : -CUDART_INF_F;
+        m_s[u] = sh.sink ? (sink_vals != nullptr ? sink_vals[u] : 0.f) : -CUDART_INF_F;
         l_s[u] = sh.sink ? 1.f : 0.f;
+        if (sh.mode == 2) {
+            const float L = stats[(size_t)t * 2 * H + 2 * u + 1];
+            fm_s[u] = stats[(size_t)t * 2 * H + 2 * u];
+            fl_s[u] = L > 0.f ? 1.f / L : 0.f;
+            l_s[u] = 1.f;                             // the weights arrive normalised: nothing is divided at the end
+            corr_s[u] = 1.f;
+        }
     }
     int first = sh.block > 0 ? (pos / sh.block) * sh.block : 0;
     if (sh.window > 0) first = max(first, pos - sh.window + 1);
@@ -164,11 +189,12 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
             const size_t at = (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * d + c;
             k_s[(size_t)jj * kstride + r] = to_float(kpool[at]);
         }
-        for (int u = tid; u < kt * G * dv; u += nt) {
-            const int jj = u / (G * dv), r = u % (G * dv), g = r / dv, c = r % dv, j = j0 + jj;
-            const size_t at = (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * dv + c;
-            v_s[(size_t)jj * G * dv + r] = to_float(vpool[at]);
-        }
+        if (sh.mode != 1)
+            for (int u = tid; u < kt * G * dv; u += nt) {
+                const int jj = u / (G * dv), r = u % (G * dv), g = r / dv, c = r % dv, j = j0 + jj;
+                const size_t at = (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * sh.v_stride + c;
+                v_s[(size_t)jj * G * dv + r] = to_float(vpool[at]);
+            }
         __syncthreads();
         for (int u = tid; u < H * KT; u += nt) {
             const int g = u / KT, jj = u % KT;
@@ -178,17 +204,32 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
                 const float* kk = k_s + (size_t)jj * kstride + (size_t)(g / rep) * d;
                 for (int c = 0; c < d; ++c) acc = fmaf(qq[c], kk[c], acc);
             }
-            raw_s[u] = acc * sh.scale;
+            acc *= sh.scale;
+            if (sh.cap > 0.f) acc = sh.cap * tanhf(acc / sh.cap);
+            if (sh.mode == 2) acc = jj < kt ? expf(acc - fm_s[g]) * fl_s[g] : 0.f;     // the head's final weight of this key
+            raw_s[u] = acc;
         }
         __syncthreads();
-        for (int h = warp; h < H; h += nwarp) {
+        if (sh.mode == 2) {
+            // the heads' weights mixed; no maximum, no correction
+            for (int u = tid; u < H * KT; u += nt) {
+                const int h = u / KT, jj = u % KT;
+                float w = raw_s[u];
+                if (talk != nullptr) {
+                    w = 0.f;
+                    for (int g = 0; g < H; ++g) w = fmaf(talk_s[h * H + g], raw_s[g * KT + jj], w);
+                }
+                p_s[u] = w;
+            }
+        }
+        for (int h = warp; h < H && sh.mode != 2; h += nwarp) {
             float s = -CUDART_INF_F;
             if (lane < kt) {
-                if (talk != nullptr) {
+                if (talk != nullptr && sh.mode == 0) {
                     s = 0.f;
                     for (int g = 0; g < H; ++g) s = fmaf(talk_s[h * H + g], raw_s[g * KT + lane], s);
                 } else {
-                    s = raw_s[h * KT + lane];
+                    s = raw_s[h * KT + lane];         // (mode 1: the head's own scores; the mixing comes after the softmax)
                 }
             }
             const float m_old = m_s[h];
@@ -205,6 +246,7 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
             if (lane < KT) p_s[h * KT + lane] = p;
         }
         __syncthreads();
+        if (sh.mode == 1) continue;
         for (int u = tid; u < H * dv; u += nt) {
             const int h = u / dv, c = u % dv;
             const float* vv = v_s + (size_t)(h / rep) * dv + c;
@@ -215,6 +257,13 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
         }
     }
     __syncthreads();
+    if (sh.mode == 1) {
+        for (int u = tid; u < H; u += nt) {
+            stats[(size_t)t * 2 * H + 2 * u] = m_s[u];
+            stats[(size_t)t * 2 * H + 2 * u + 1] = l_s[u];
+        }
+        return;
+    }
     if (inv_v != nullptr) {
         const int hv = dv >> 1;
         for (int u = tid; u < H * hv; u += nt) {
@@ -731,7 +780,8 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
                                       const int* page_table, int table_stride, const float* talk, const float* inv_v,
                                       void* out, int T, int H, int G, int d, int dv, float scale, int block, int sink,
                                       int one_row, int max_keys, int n_chunks, float* partial, long long partial_floats,
-                                      int window, cudaStream_t stream) {
+                                      int window, float cap, const float* sink_vals, int mix_after, int v_in_keys,
+                                      float* stats, long long stats_floats, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) return fail("talk_attention: %d query heads do not divide over %d key/value heads", H, G);
     if (d <= 0 || dv <= 0) return fail("talk_attention: key size %d, value size %d", d, dv);
@@ -739,7 +789,14 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     if (q_row_elems < H * d) return fail("talk_attention: query rows of %d elements are too short", q_row_elems);
     if (block < 0) return fail("talk_attention: block size %d", block);
     if (window < 0) return fail("talk_attention: window %d", window);
-    if (dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
+    if (v_in_keys && (dv > d || inv_v != nullptr)) return fail("talk_attention: values of %d features do not lie in keys of %d", dv, d);
+    if (sink_vals != nullptr && !sink) return fail("talk_attention: sink values without a sink");
+    const bool two_pass = mix_after && talk != nullptr;       // (without a matrix there is nothing to mix: one pass)
+    if (two_pass && (stats == nullptr || stats_floats < (long long)T * 2 * H))
+        return fail("talk_attention: heads mixed after the softmax need %lld floats for the rows' maxima and denominators", (long long)T * 2 * H);
+    if (v_in_keys) vpool = kpool;
+    const bool mma_takes = cap == 0.f && sink_vals == nullptr && !two_pass && !v_in_keys;
+    if (mma_takes && dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
         (((uintptr_t)q_rows | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0) {
         size_t mma_bytes = 0;
         TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
@@ -765,6 +822,7 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     size_t bytes = 0;
     TalkShape sh;
     sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale; sh.window = window;
+    sh.cap = cap; sh.mode = 0; sh.v_stride = v_in_keys ? d : dv;
     sh.kt = talk_plain_tile(H, G, d, dv, &bytes);
     if (sh.kt == 0) return fail("talk_attention: heads of these sizes do not fit shared memory (%d x %d, %d x %d)", H, d, G, dv);
     const dim3 grid(T), block_dim(256);
@@ -775,9 +833,14 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
             if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
             most_f = bytes;
         }
-        return launch_kernel("talk_attention", talk_attention_plain_kernel<float>, grid, block_dim, bytes, stream, 1,
-                             (const float*)q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, (const float*)kpool,
-                             (const float*)vpool, page_table, table_stride, talk, inv_v, (float*)out, sh);
+        for (int pass = two_pass ? 1 : 0; pass <= (two_pass ? 2 : 0); ++pass) {
+            sh.mode = pass;
+            if (launch_kernel("talk_attention", talk_attention_plain_kernel<float>, grid, block_dim, bytes, stream, 1,
+                              (const float*)q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, (const float*)kpool,
+                              (const float*)vpool, page_table, table_stride, talk, inv_v, (float*)out, sink_vals, stats, sh))
+                return 1;
+        }
+        return 0;
     }
     if (dtype == JANIS_BF16) {
         static size_t most_b = 0;
@@ -786,9 +849,14 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
             if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
             most_b = bytes;
         }
-        return launch_kernel("talk_attention", talk_attention_plain_kernel<bf16>, grid, block_dim, bytes, stream, 1,
-                             (const bf16*)q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool,
-                             (const bf16*)vpool, page_table, table_stride, talk, inv_v, (bf16*)out, sh);
+        for (int pass = two_pass ? 1 : 0; pass <= (two_pass ? 2 : 0); ++pass) {
+            sh.mode = pass;
+            if (launch_kernel("talk_attention", talk_attention_plain_kernel<bf16>, grid, block_dim, bytes, stream, 1,
+                              (const bf16*)q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool,
+                              (const bf16*)vpool, page_table, table_stride, talk, inv_v, (bf16*)out, sink_vals, stats, sh))
+                return 1;
+        }
+        return 0;
     }
     return fail("talk_attention: unknown dtype %d", dtype);
 }

@@ -1,5 +1,6 @@
-// Rows of the residual stream and of a layer's branches: the Dynamic Tanh norm, the norm-and-accumulate of branches
-// that run side by side, and a sigmoid gate on the heads of an attention.  All arithmetic is float.
+// Rows of the residual stream and of a layer's branches: the Dynamic Tanh norm, the RMS norm in groups that follows a
+// scaled residual sum, the norm-and-accumulate of branches that run side by side, and a sigmoid gate on the heads of
+// an attention.  All arithmetic is float.
 #include "common.cuh"
 
 #include <math_constants.h>
@@ -52,15 +53,74 @@ rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* __restrict__ w, 
     }
 }
 
-// x[t, c] *= sigmoid(rows[t, g_off + c])
+// RMS norm in groups: the row is cut into `groups` equal runs, each divided by sqrt(mean(run^2) + eps), and the whole
+// multiplied by w.  With a residual: v = alpha h[r] + res[r], h[r] = norm(v) (the stream itself is normed, in place)
+// and y[r] = h[r] rounded; without: y[r] = norm(h[src]) with src = rows[r] (or r), h untouched.
+// A group's sum runs over the lanes of its warps and then over its warps in index order.
+template <typename TR, typename TO>
+__global__ void __launch_bounds__(256)
+group_norm_kernel(float* __restrict__ h, const TR* __restrict__ res, const int* __restrict__ rows, float alpha,
+                  const float* __restrict__ w, float eps, int groups, TO* __restrict__ y, int H) {
+    extern __shared__ float gn_smem[];
+    float* row_s = gn_smem;                 // the row
+    float* inv_s = row_s + H;               // 1 / rms of each group
+    float* scratch = inv_s + groups;        // a partial sum per warp
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int src = rows != nullptr ? rows[r] : r;
+    float* hr = h + (size_t)src * H;
+    for (int i = tid; i < H; i += blockDim.x) {
+        float v = hr[i];
+        if (res != nullptr) v = fmaf(alpha, v, to_float(res[(size_t)r * H + i]));
+        row_s[i] = v;
+    }
+    const int gs = H / groups;
+    const int wpg = nwarp / groups > 0 ? nwarp / groups : 1;      // warps that share a group
+    const int gpr = nwarp / wpg;                                  // groups summed side by side
+    for (int g0 = 0; g0 < groups; g0 += gpr) {
+        __syncthreads();
+        const int g = g0 + warp / wpg, wi = warp % wpg;
+        float ss = 0.f;
+        if (g < groups && warp < gpr * wpg)
+            for (int i = wi * 32 + lane; i < gs; i += wpg * 32) {
+                const float v = row_s[g * gs + i];
+                ss = fmaf(v, v, ss);
+            }
+        ss = warp_sum(ss);
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        if (tid < gpr && g0 + tid < groups) {
+            float tot = 0.f;
+            for (int k = 0; k < wpg; ++k) tot += scratch[tid * wpg + k];
+            inv_s[g0 + tid] = 1.f / sqrtf(tot / (float)gs + eps);
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < H; i += blockDim.x) {
+        const float v = row_s[i] * inv_s[i / gs] * w[i];
+        if (res != nullptr) hr[i] = v;
+        if (y != nullptr) y[(size_t)r * H + i] = from_float<TO>(v);
+    }
+}
+
+// y = h rounded to the activation type: what a sublayer reads when it reads the stream itself
+__global__ void __launch_bounds__(256) round_rows_kernel(const float* __restrict__ h, bf16* __restrict__ y, size_t n) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = __float2bfloat16_rn(h[i]);
+}
+
+// x[t, c] *= sigmoid(rows[t, g_off + c / per]): a gate per element (per = 1) or per run of `per` elements (a head)
 template <typename T>
 __global__ void __launch_bounds__(256)
-sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ rows, int row_elems, int g_off, int width, size_t n) {
+sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ rows, int row_elems, int g_off, int width, int per, size_t n) {
     grid_dependents_launch();
     grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / width;
-        const int c = (int)(i % width);
+        const int c = (int)(i % width) / per;
         const float g = to_float(rows[t * row_elems + g_off + c]);
         x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-g)));
     }
@@ -270,17 +330,52 @@ JANIS_EXPORT int janis_rmsnorm_accumulate(const void* x, int dtype, const float*
 }
 
 JANIS_EXPORT int janis_sigmoid_gate(void* x, const void* rows, int dtype, int row_elems, int g_off, int T, int width,
-                                    cudaStream_t stream) {
+                                    int per, cudaStream_t stream) {
     if (T <= 0 || width <= 0) return 0;
-    if (g_off < 0 || g_off + width > row_elems) return fail("sigmoid_gate: %d gates at %d do not fit rows of %d", width, g_off, row_elems);
+    if (per <= 0 || width % per) return fail("sigmoid_gate: runs of %d elements do not divide %d", per, width);
+    if (g_off < 0 || g_off + width / per > row_elems) return fail("sigmoid_gate: %d gates at %d do not fit rows of %d", width / per, g_off, row_elems);
     const size_t n = (size_t)T * width;
     if (dtype == JANIS_F32)
         return launch_kernel("sigmoid_gate", sigmoid_gate_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, 1, (float*)x,
-                             (const float*)rows, row_elems, g_off, width, n);
+                             (const float*)rows, row_elems, g_off, width, per, n);
     if (dtype == JANIS_BF16)
         return launch_kernel("sigmoid_gate", sigmoid_gate_kernel<bf16>, dim3(flat_grid(n)), dim3(256), 0, stream, 1, (bf16*)x,
-                             (const bf16*)rows, row_elems, g_off, width, n);
+                             (const bf16*)rows, row_elems, g_off, width, per, n);
     return fail("sigmoid_gate: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_group_norm(float* h, const void* res, int res_dtype, const int* rows, float alpha, const float* w,
+                                  float eps, int groups, void* y, int y_dtype, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (groups <= 0 || H % groups) return fail("group_norm: %d groups do not divide a row of %d", groups, H);
+    if (res != nullptr && rows != nullptr) return fail("group_norm: a residual is added to all rows, not to chosen ones");
+    if (res == nullptr && y == nullptr) return fail("group_norm: nothing to write");
+    const size_t bytes = ((size_t)H + groups + 32) * sizeof(float);
+    if (bytes > 200 * 1024) return fail("group_norm: a row of %d does not fit shared memory", H);
+    const dim3 grid(R), block(H >= 1024 ? 256 : 128);
+#define JANIS_GN(TR, TO)                                                                                               \
+    {                                                                                                                  \
+        static size_t most = 0;                                                                                        \
+        if (bytes > most && bytes > 48 * 1024) {                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(group_norm_kernel<TR, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
+            if (e != cudaSuccess) return fail("group_norm: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e)); \
+            most = bytes;                                                                                              \
+        }                                                                                                              \
+        return launch_kernel("group_norm", group_norm_kernel<TR, TO>, grid, block, bytes, stream, 1, h, (const TR*)res, rows, \
+                             alpha, w, eps, groups, (TO*)y, H);                                                        \
+    }
+    const int rd = res != nullptr ? res_dtype : JANIS_F32, yd = y != nullptr ? y_dtype : JANIS_F32;
+    if (rd == JANIS_F32 && yd == JANIS_F32) JANIS_GN(float, float)
+    if (rd == JANIS_F32 && yd == JANIS_BF16) JANIS_GN(float, bf16)
+    if (rd == JANIS_BF16 && yd == JANIS_F32) JANIS_GN(bf16, float)
+    if (rd == JANIS_BF16 && yd == JANIS_BF16) JANIS_GN(bf16, bf16)
+#undef JANIS_GN
+    return fail("group_norm: unknown dtypes %d, %d", res_dtype, y_dtype);
+}
+
+JANIS_EXPORT int janis_round_rows(const float* h, void* y, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    return launch_kernel("round_rows", round_rows_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, 1, h, (bf16*)y, n);
 }
 
 JANIS_EXPORT int janis_moe_route(const float* z, const float* correction, int T, int E, int n_groups, int keep, int top,

@@ -39,7 +39,7 @@ causal_conv_silu_kernel(const T* __restrict__ rows, int row_elems, int col_off, 
                         const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
                         const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
-                        const int* __restrict__ seq_end, T* __restrict__ out, int n_tok, int tokens_per_cta) {
+                        const int* __restrict__ seq_end, T* __restrict__ out, int n_tok, int tokens_per_cta, int act) {
     grid_dependents_launch();
     grid_dependency_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -47,7 +47,7 @@ causal_conv_silu_kernel(const T* __restrict__ rows, int row_elems, int col_off, 
     float wk[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) wk[j] = j < K ? w[(size_t)c * K + K - 1 - j] : 0.f;      // wk[j]: the tap j tokens back
-    const float b = bias[c];
+    const float b = bias != nullptr ? bias[c] : 0.f;
     const int t_end = min(n_tok, ((int)blockIdx.x + 1) * tokens_per_cta);
     for (int t = blockIdx.x * tokens_per_cta; t < t_end; ++t) {
         const int s = tok_seq[t], slot = seq_slot[s], i = t - seq_first_row[s];
@@ -65,7 +65,7 @@ causal_conv_silu_kernel(const T* __restrict__ rows, int row_elems, int col_off, 
             xs[j] = x;
             acc = fmaf(wk[j], x, acc);
         }
-        out[(size_t)t * C + c] = from_float<T>(silu_f(acc));
+        out[(size_t)t * C + c] = from_float<T>(act ? silu_f(acc) : acc);
         if (alone && st != nullptr) {                        // (i == 0: xs[j] is the input j tokens back; this thread alone touches (slot, c))
 #pragma unroll
             for (int j = 0; j < 15; ++j) {
@@ -456,12 +456,12 @@ template <typename T>
 static int conv_launch(const void* rows, int row_elems, int col_off, int C, int K, const float* w, const float* bias,
                        float* state, const int* tok_seq, const int* seq_slot, const int* seq_first_row,
                        const int* seq_start, const int* seq_end, int n_tok, int n_seq, int one_token, void* out,
-                       cudaStream_t stream) {
+                       int act, cudaStream_t stream) {
     const int by = (C + 255) / 256, tpc = n_tok >= 1024 ? 8 : 1;
     if (by > 65535) return fail("causal_conv_silu: too many channels (%d)", C);
     if (launch_kernel("causal_conv_silu", causal_conv_silu_kernel<T>, dim3((n_tok + tpc - 1) / tpc, by), dim3(256), 0, stream, 1,
                       (const T*)rows, row_elems, col_off, C, K, w, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
-                      seq_end, (T*)out, n_tok, tpc))
+                      seq_end, (T*)out, n_tok, tpc, act))
         return 1;
     if (K <= 1 || one_token) return 0;
     return launch_kernel("conv_state_update", conv_state_update_kernel<T>, dim3(n_seq, by < 64 ? by : 64), dim3(256), 0, stream, 1,
@@ -472,17 +472,36 @@ JANIS_EXPORT int janis_causal_conv_silu(const void* rows, int dtype, int row_ele
                                         const float* w, const float* bias, float* state, const int* tok_seq,
                                         const int* seq_slot, const int* seq_first_row, const int* seq_start,
                                         const int* seq_end, int n_tok, int n_seq, int one_token, void* out,
-                                        cudaStream_t stream) {
+                                        int act, cudaStream_t stream) {
     if (n_tok <= 0 || n_seq <= 0) return 0;
     if (K < 1 || K > 16) return fail("causal_conv_silu: %d taps (1 to 16 are taken)", K);
     if (C <= 0 || col_off < 0 || col_off + C > row_elems) return fail("causal_conv_silu: channels %d at %d do not fit rows of %d", C, col_off, row_elems);
     if (dtype == JANIS_F32)
         return conv_launch<float>(rows, row_elems, col_off, C, K, w, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
-                                  seq_end, n_tok, n_seq, one_token, out, stream);
+                                  seq_end, n_tok, n_seq, one_token, out, act, stream);
     if (dtype == JANIS_BF16)
         return conv_launch<bf16>(rows, row_elems, col_off, C, K, w, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
-                                 seq_end, n_tok, n_seq, one_token, out, stream);
+                                 seq_end, n_tok, n_seq, one_token, out, act, stream);
     return fail("causal_conv_silu: unknown dtype %d", dtype);
+}
+
+// The kept inputs of a filter brought up to date from rows that another kernel filtered (one that shifts them itself for
+// sequences that bring a single token).
+JANIS_EXPORT int janis_conv_state_update(const void* rows, int dtype, int row_elems, int col_off, int C, int K, float* state,
+                                         const int* seq_slot, const int* seq_first_row, const int* seq_start,
+                                         const int* seq_end, int n_seq, cudaStream_t stream) {
+    if (n_seq <= 0 || K <= 1) return 0;
+    if (K > 16) return fail("conv_state_update: %d taps (1 to 16 are taken)", K);
+    if (C <= 0 || col_off < 0 || col_off + C > row_elems) return fail("conv_state_update: channels %d at %d do not fit rows of %d", C, col_off, row_elems);
+    const int by = (C + 255) / 256;
+    const dim3 grid(n_seq, by < 64 ? by : 64), block(256);
+    if (dtype == JANIS_F32)
+        return launch_kernel("conv_state_update", conv_state_update_kernel<float>, grid, block, 0, stream, 1, (const float*)rows,
+                             row_elems, col_off, C, K, state, seq_slot, seq_first_row, seq_start, seq_end);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("conv_state_update", conv_state_update_kernel<bf16>, grid, block, 0, stream, 1, (const bf16*)rows,
+                             row_elems, col_off, C, K, state, seq_slot, seq_first_row, seq_start, seq_end);
+    return fail("conv_state_update: unknown dtype %d", dtype);
 }
 
 template <typename T, bool PER_STATE>

@@ -138,12 +138,18 @@ def mixers():
         lib = build.mixers_library()
         P, I, F = c_void_p, c_int, c_float
         lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
-        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, F, P, I, I, P, c_longlong, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
-        lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P, P]
+        lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P, I, P]
+        lib.janis_conv_state_update.argtypes = [P, I, I, I, I, I, P, P, P, P, P, I, P]
+        lib.janis_qkv_conv_norm_store.argtypes = [P, I, I, I, I, I, I, I, I, P, P, P, P, I, F, P, P, P, P, P, P, P, P, P, P, I, P]
+        lib.janis_latent_rotate_store.argtypes = [P, I, I, I, I, I, I, I, I, I, P, F, P, F, P, P, P, P, P, P, I, P]
+        lib.janis_head_linear.argtypes = [P, I, I, I, I, P, P, I, I, I, I, I, I, I, P]
+        lib.janis_group_norm.argtypes = [P, P, I, P, F, P, F, I, P, I, I, I, P]
+        lib.janis_round_rows.argtypes = [P, P, ctypes.c_size_t, P]
         lib.janis_selective_scan.argtypes = [P, I, I, I, P, I, I, P, P, I, P, I, I, I, P, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, P, P]
         lib.janis_selective_scan_set_lanes.argtypes = [I]
         lib.janis_selective_scan_set_lanes.restype = None
@@ -152,7 +158,7 @@ def mixers():
         lib.janis_gate_group_norm.argtypes = [P, P, I, I, I, P, F, I, P, I, I, P]
         lib.janis_dyt_norm.argtypes = [P, P, I, P, F, P, P, P, I, I, I, P]
         lib.janis_rmsnorm_accumulate.argtypes = [P, I, P, F, F, P, I, I, I, P]
-        lib.janis_sigmoid_gate.argtypes = [P, P, I, I, I, I, I, P]
+        lib.janis_sigmoid_gate.argtypes = [P, P, I, I, I, I, I, I, P]
         lib.janis_moe_route.argtypes = [P, P, I, I, I, I, I, F, I, P, P]
         lib.janis_moe_expert_act.argtypes = [P, I, P, I, I, F, I, F, F, P, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
@@ -802,7 +808,8 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
                    d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False,
-                   max_keys: int = 0, n_chunks: int = 1, scratch=None, window: int = 0):
+                   max_keys: int = 0, n_chunks: int = 1, scratch=None, window: int = 0, cap: float = 0.0,
+                   sink_values=None, mix_after: bool = False, values_in_keys: bool = False, stats=None):
     """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
     own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
     alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
@@ -812,12 +819,21 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
     or 8 rows of the step; one_row=True, for decode steps, gives every row a CTA of its own); everything else
     runs the plain kernel, which is exact 32-bit for float32.  A decode step on the tensor cores may cut every row's
     keys over n_chunks CTAs (max_keys: a bound on the keys a row sees; scratch: float32, at least
-    `talk_attention_scratch_floats`) whose shares a second kernel puts together."""
+    `talk_attention_scratch_floats`) whose shares a second kernel puts together.
+    cap > 0: every scaled score becomes cap tanh(score / cap) first.  sink_values [H] float32 (with sink): exp of
+    head h's value joins its denominator instead of 1.  mix_after: talk mixes the heads' weights after the softmax
+    instead of their scores before it, which takes two passes over the keys and `stats`, float32 of at least
+    `talk_attention_stats_floats` (the rows' maxima and denominators between the passes).  values_in_keys: the
+    values are the first dv features of the cached keys (vpool is not read and may be None)."""
     T = q_rows.shape[0]
     _t(q_rows, "q_rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
     _t(kpool, "kpool", q_rows.dtype, (n_pages, G, PAGE, d))
-    _t(vpool, "vpool", q_rows.dtype, (n_pages, G, PAGE, dv))
+    if not values_in_keys:
+        _t(vpool, "vpool", q_rows.dtype, (n_pages, G, PAGE, dv))
+    if sink_values is not None and not sink:
+        raise KernelError("talk_attention: sink values without a sink")
+    two_pass = bool(mix_after) and talk is not None
     _t(page_table, "page_table", torch.int32, (None, None))
     _t(out, "out", q_rows.dtype, (T, H * dv))
     if tok_pos.numel() < T or tok_seq.numel() < T:
@@ -825,15 +841,25 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
     lib = mixers()
     _check(lib, lib.janis_talk_attention(
         q_rows.data_ptr(), _DT[q_rows.dtype], q_rows.shape[1], _t(tok_pos, "tok_pos", torch.int32),
-        _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32), kpool.data_ptr(), vpool.data_ptr(),
-        page_table.data_ptr(), page_table.shape[1],
+        _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32), kpool.data_ptr(),
+        None if values_in_keys else vpool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None,
         _t(inv_v, "inv_v", torch.float32, (dv // 2,)) if inv_v is not None else None, out.data_ptr(), T, H, G, d, dv,
         float(scale), int(block), 1 if sink else 0, 1 if one_row else 0, int(max_keys), int(n_chunks),
         _t(scratch, "scratch", torch.float32) if scratch is not None else None,
-        scratch.numel() if scratch is not None else 0, int(window), _stream()),
-        kernels=2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1)
+        scratch.numel() if scratch is not None else 0, int(window), float(cap),
+        _t(sink_values, "sink_values", torch.float32, (H,)) if sink_values is not None else None,
+        1 if mix_after else 0, 1 if values_in_keys else 0,
+        _t(stats, "stats", torch.float32) if stats is not None else None, stats.numel() if stats is not None else 0,
+        _stream()),
+        kernels=(2 if two_pass else 1) *
+                (2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1))
     return out
+
+
+def talk_attention_stats_floats(T: int, H: int) -> int:
+    """What `talk_attention(mix_after=True)` keeps between its passes: a maximum and a denominator per row and head."""
+    return 2 * T * H
 
 
 def talk_attention_scratch_floats(T: int, n_chunks: int, H: int, dv: int) -> int:
@@ -912,8 +938,9 @@ def dyt_norm(h, res, alpha: float, weight, bias, out, rows=None):
 
 
 def causal_conv_silu(rows, col_off: int, channels: int, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
-                     seq_end, n_seq: int, out, one_token: bool = False):
-    """out[t, c] = silu(bias[c] + sum_j weight[c, K-1-j] x[t-j, c]) over the channels rows[:, col_off : col_off +
+                     seq_end, n_seq: int, out, one_token: bool = False, act: bool = True):
+    """out[t, c] = silu(bias[c] + sum_j weight[c, K-1-j] x[t-j, c]) (act=False: without the silu; bias None: without
+    one) over the channels rows[:, col_off : col_off +
     channels] of each sequence's tokens; inputs before the step come from state float32 [slots, max(K-1, 1), channels]
     (the last K-1 inputs of each slot), which is brought up to date: by the same kernel for sequences that bring one
     token, by a second kernel for the others (one_token=True: every sequence brings one, a decode step, and the
@@ -931,10 +958,11 @@ def causal_conv_silu(rows, col_off: int, channels: int, weight, bias, state, tok
     lib = mixers()
     _check(lib, lib.janis_causal_conv_silu(rows.data_ptr(), _DT[rows.dtype], width, int(col_off), int(channels), K,
                                            _t(weight, "weight", torch.float32, (channels, K)),
-                                           _t(bias, "bias", torch.float32, (channels,)), state.data_ptr(),
+                                           _t(bias, "bias", torch.float32, (channels,)) if bias is not None else None,
+                                           state.data_ptr(),
                                            tok_seq.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(),
                                            seq_start.data_ptr(), seq_end.data_ptr(), T, n_seq, 1 if one_token else 0,
-                                           _t(out, "out", rows.dtype, (T, channels)), _stream()),
+                                           _t(out, "out", rows.dtype, (T, channels)), 1 if act else 0, _stream()),
            kernels=2 if K > 1 and not one_token else 1)
     return out
 
@@ -1025,13 +1053,121 @@ def rmsnorm_accumulate(x, weight, eps: float, scale: float, acc, first: bool = F
     return acc
 
 
-def sigmoid_gate(x, rows, g_off: int):
-    """x[t, c] *= sigmoid(rows[t, g_off + c]) in place; x [T, n], rows [T, >= g_off + n] of x's dtype."""
+def sigmoid_gate(x, rows, g_off: int, per: int = 1):
+    """x[t, c] *= sigmoid(rows[t, g_off + c // per]) in place: a gate per element, or per run of `per` elements (a
+    head); x [T, n], rows [T, >= g_off + n / per] of x's dtype."""
     T, n = x.shape
     lib = mixers()
     _check(lib, lib.janis_sigmoid_gate(_t(x, "x", _FLOATS, (T, n)), _t(rows, "rows", x.dtype, (T, None)), _DT[x.dtype],
-                                       rows.shape[1], int(g_off), T, n, _stream()))
+                                       rows.shape[1], int(g_off), T, n, int(per), _stream()))
     return x
+
+
+def group_norm(h, res, alpha: float, weight, eps: float, groups: int, out, rows=None):
+    """RMS norm in `groups` equal runs of the row, each divided by its own sqrt(mean(run^2) + eps), the whole times
+    weight.  With res: h <- norm(alpha h + res) on the float32 stream in place, and out (when given) = h rounded.
+    Without: out = norm(h[rows]) (all rows when `rows` is None), h untouched."""
+    R = out.shape[0] if out is not None else h.shape[0]
+    H = h.shape[1]
+    lib = mixers()
+    _check(lib, lib.janis_group_norm(_t(h, "h", torch.float32, (None, H)),
+                                     _t(res, "res", _FLOATS, (R, H)) if res is not None else None,
+                                     _DT[res.dtype] if res is not None else 0,
+                                     _t(rows, "rows", torch.int32, (R,)) if rows is not None else None, float(alpha),
+                                     _t(weight, "weight", torch.float32, (H,)), float(eps), int(groups),
+                                     _t(out, "out", _FLOATS, (R, H)) if out is not None else None,
+                                     _DT[out.dtype] if out is not None else 0, R, H, _stream()))
+    return out
+
+
+def round_rows(h, out):
+    """out = h rounded to bfloat16 (h float32, same shape)."""
+    lib = mixers()
+    _check(lib, lib.janis_round_rows(_t(h, "h", torch.float32), _t(out, "out", torch.bfloat16, tuple(h.shape)),
+                                     h.numel(), _stream()))
+    return out
+
+
+def qkv_conv_norm_store(rows, H: int, G: int, d: int, dv: int, conv_w, conv_state, wq, wk, v_unit: bool, eps: float,
+                        tok_pos, tok_seq, seq_slot, seq_first_row, seq_start, seq_end, n_seq: int, q_out, kpool, vpool,
+                        page_table, one_token: bool = False):
+    """What an attention does to its projections before it caches them.  rows [T, >= H d + G d + G dv] holds q | k | v.
+    conv_w float32 [channels, K] (None: no filter): every channel is filtered over time, y[t] = sum_j conv_w[c, K-1-j]
+    x[t-j]; inputs before the step come from conv_state float32 [slots, K-1, channels], which is brought up to date
+    (as `causal_conv_silu` does it).  wq [H d], wk [G d] float32 (None: no norm): RMS norm over the whole of q, of k.
+    v_unit: every value head is divided by its root mean square.  q goes to q_out [T, H d], k and v into the cache
+    line at the tokens' positions; sequences without a slot store nothing."""
+    T, width = rows.shape
+    C = H * d + G * (d + dv)
+    K = conv_w.shape[1] if conv_w is not None else 0
+    _t(rows, "rows", _FLOATS, (T, None))
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", rows.dtype, (n_pages, G, PAGE, d))
+    _t(vpool, "vpool", rows.dtype, (n_pages, G, PAGE, dv))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    for name, tab, n in (("tok_pos", tok_pos, T), ("tok_seq", tok_seq, T), ("seq_slot", seq_slot, n_seq),
+                         ("seq_first_row", seq_first_row, n_seq), ("seq_start", seq_start, n_seq), ("seq_end", seq_end, n_seq)):
+        _t(tab, name, torch.int32)
+        if tab.numel() < n:
+            raise KernelError(f"qkv_conv_norm_store: {name} shorter than the step")
+    if K > 1:
+        _t(conv_state, "conv_state", torch.float32, (None, K - 1, C))
+    lib = mixers()
+    _check(lib, lib.janis_qkv_conv_norm_store(
+        rows.data_ptr(), _DT[rows.dtype], width, T, H, G, d, dv, K,
+        _t(conv_w, "conv_w", torch.float32, (C, K)) if conv_w is not None else None,
+        conv_state.data_ptr() if K > 1 else None,
+        _t(wq, "wq", torch.float32, (H * d,)) if wq is not None else None,
+        _t(wk, "wk", torch.float32, (G * d,)) if wk is not None else None, 1 if v_unit else 0, float(eps),
+        tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
+        seq_end.data_ptr(), _t(q_out, "q_out", rows.dtype, (T, H * d)), kpool.data_ptr(), vpool.data_ptr(),
+        page_table.data_ptr(), page_table.shape[1], _stream()))
+    if K > 1 and not one_token:
+        _check(lib, lib.janis_conv_state_update(rows.data_ptr(), _DT[rows.dtype], width, 0, C, K, conv_state.data_ptr(),
+                                                seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
+                                                seq_end.data_ptr(), n_seq, _stream()))
+    return q_out
+
+
+def latent_rotate_store(rows, lat_off: int, H: int, d: int, dr: int, R: int, wc, eps: float, inv_freq, amp: float,
+                        tok_pos, tok_seq, seq_slot, qfull, kpool, page_table, rot: int | None = None):
+    """rows [T, ...]: H query heads of d + dr at 0, the compressed row [c (R) | r (dr)] at lat_off.  c is RMS-normed with
+    wc, r and every query head's last dr features are turned by the token's position (pairs 2i, 2i + 1 of the first
+    `rot` of them, all when None, angle pos * inv_freq[i], sine and cosine times amp).  [norm(c) | turn(r)] becomes the key of the line's single head at the
+    token's position (kpool [pages, 1, PAGE, R + dr]); the turned query parts go to qfull[t, h, R:], whose first R
+    features per head are left for the absorbed queries."""
+    T, width = rows.shape
+    _t(rows, "rows", _FLOATS, (T, None))
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", rows.dtype, (n_pages, 1, PAGE, R + dr))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("latent_rotate_store: position tables shorter than the step")
+    lib = mixers()
+    _check(lib, lib.janis_latent_rotate_store(
+        rows.data_ptr(), _DT[rows.dtype], width, int(lat_off), T, H, d, dr, dr if rot is None else int(rot), R,
+        _t(wc, "wc", torch.float32, (R,)), float(eps), _t(inv_freq, "inv_freq", torch.float32, (dr // 2,)), float(amp),
+        _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32),
+        _t(qfull, "qfull", rows.dtype, (T, H * (R + dr))), kpool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        _stream()))
+    return qfull
+
+
+def head_linear(x, x_head: int, x_off: int, w, out, o_head: int, o_off: int):
+    """out[t, h * o_head + o_off + o] = sum_i w[h, o, i] x[t, h * x_head + x_off + i]: a product per head with a
+    matrix of its own.  x [T, >= H x_head], w [H, O, I], out [T, >= H o_head], all of one dtype; float accumulation
+    in an order that depends on I alone."""
+    T = x.shape[0]
+    Hn, O, I = w.shape
+    _t(x, "x", _FLOATS, (T, None))
+    _t(w, "w", x.dtype, (Hn, O, I))
+    _t(out, "out", x.dtype, (T, None))
+    if (Hn - 1) * x_head + x_off + I > x.shape[1] or (Hn - 1) * o_head + o_off + O > out.shape[1]:
+        raise KernelError("head_linear: the heads do not fit the rows")
+    lib = mixers()
+    _check(lib, lib.janis_head_linear(x.data_ptr(), _DT[x.dtype], x.shape[1], int(x_head), int(x_off), w.data_ptr(),
+                                      out.data_ptr(), out.shape[1], int(o_head), int(o_off), T, Hn, I, O, _stream()))
+    return out
 
 
 def moe_route(z, correction, n_experts: int, group_count: int, group_keep: int, top: int, scale: float,

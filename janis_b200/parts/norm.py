@@ -1,4 +1,4 @@
-"""Norms of the residual stream: RMS norm with a weight offset, and Dynamic Tanh.
+"""Norms of the residual stream: RMS norm with a weight offset, Dynamic Tanh, and the RMS norm in groups.
 
 y = x / sqrt(mean(x^2) + eps) * (offset + w).  Gemma2 stores w and uses 1 + w
 (`gemma/gemma.go:22-28`); offset 0 is the usual RMS norm (`qwen/norm.go:10-27`).
@@ -7,6 +7,10 @@ sum of squares, the root and offset + w are float32 whatever the model's dtype.
 
 `DynamicTanh` takes no statistics of the row: y = tanh(alpha x) * w + b with a stored scalar alpha and vectors w
 and b, element by element, in float32.
+
+`GroupRMSNorm` cuts the row into `groups` equal runs and divides each by its own sqrt(mean(run^2) + eps) before the
+whole is multiplied by w.  It can norm the stream itself after a scaled residual sum (`scaled_add`: h <- N(a h + r)),
+which is what a block that norms after the sum needs.
 """
 from __future__ import annotations
 
@@ -79,6 +83,32 @@ class DynamicTanh(Norm):
 
     def residual_add(self, h, r, ctx: StepContext, next_norm: Norm | None = None, out=None):
         raise NotImplementedError("Dynamic Tanh stands before a sublayer, not after one")
+
+
+class GroupRMSNorm(Norm):
+    def __init__(self, width: int, eps: float, groups: int, weight_name: str, init_std: float = 0.1, init_mean: float = 1.0):
+        if groups < 1 or width % groups:
+            raise ValueError(f"{groups} groups do not divide a width of {width}")
+        self.width, self.eps, self.groups = width, float(eps), int(groups)
+        self.weight_name = weight_name
+        self.init_std, self.init_mean = init_std, init_mean
+        self.weight = None          # float32
+
+    def tensor_specs(self):
+        return {self.weight_name: TensorSpec((self.width,), init_std=self.init_std, init_mean=self.init_mean)}
+
+    def load(self, store, rt: Runtime):
+        self.weight = store.get(self.weight_name).to(torch.float32).contiguous()
+
+    def forward(self, x, ctx: StepContext, out, rows=None):
+        return ctx.rt.ops.group_norm(x, None, 1.0, self.weight, self.eps, self.groups, out, rows)
+
+    def scaled_add(self, h, r, alpha: float, ctx: StepContext, out=None):
+        """h <- self(alpha h + r) on the float32 stream in place; out (when given) = the new h in the activation type."""
+        return ctx.rt.ops.group_norm(h, r, alpha, self.weight, self.eps, self.groups, out)
+
+    def residual_add(self, h, r, ctx: StepContext, next_norm: Norm | None = None, out=None):
+        raise NotImplementedError("the norm in groups norms the stream itself (scaled_add), not a sublayer's output")
 
 
 def plain_residual_add(h, r, ctx: StepContext, next_norm: Norm | None = None, out=None):

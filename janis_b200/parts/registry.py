@@ -39,19 +39,23 @@ def make(family: str, kind: str, **params):
 
 def _register_builtin() -> None:
     from .attention import SoftmaxAttention
-    from .block import PreNormBlock, SandwichBlock
+    from .block import PostNormBlock, PreNormBlock, SandwichBlock
     from .embedding import Embedding, LMHead
     from .feedforward import DenseMLP, GatedMLP
+    from .filtered_attention import FilteredAttention
+    from .latent_attention import LatentAttention
     from .linear_attention import GatedLinearAttention
     from .talking_attention import TalkingHeadsAttention
     from .moe import RoutedExperts
-    from .norm import DynamicTanh, RMSNorm
+    from .norm import DynamicTanh, GroupRMSNorm, RMSNorm
     from .parallel import ParallelMixers
     from .state_space import DualityMixer, SelectiveScanMixer
     from .position import NoPosition, RotaryEncoding
 
     register("mixer", "softmax_attention", SoftmaxAttention)
     register("mixer", "talking_heads_attention", TalkingHeadsAttention)   # heads mixed before the softmax, sink, block mask
+    register("mixer", "filtered_attention", FilteredAttention)             # filtered and normed projections, capped scores, weights mixed after the softmax
+    register("mixer", "latent_attention", LatentAttention)                 # one compressed row cached per position, a sink per head, a window
     register("mixer", "gated_linear_attention", GatedLinearAttention)     # a matrix of state per head, decays per key channel
     register("mixer", "selective_scan", SelectiveScanMixer)               # a state per channel, step sizes through a low rank
     register("mixer", "state_space_duality", DualityMixer)                # a scalar decay per head, grouped B and C
@@ -61,10 +65,12 @@ def _register_builtin() -> None:
     register("feed_forward", "routed_experts", RoutedExperts)             # a router over small gated experts, a shared one
     register("norm", "rms_norm", RMSNorm)
     register("norm", "dynamic_tanh", DynamicTanh)
+    register("norm", "group_rms_norm", GroupRMSNorm)       # each run of the row by its own root mean square; norms the stream in place
     register("position", "rotary", RotaryEncoding)
     register("position", "none", NoPosition)
     register("block", "sandwich", SandwichBlock)
     register("block", "pre_norm", PreNormBlock)
+    register("block", "post_norm", PostNormBlock)          # the norm after the sum, the stream scaled by a constant
     register("embedding", "scaled_table", Embedding)       # rows of a table times a constant (1 for most models)
     register("head", "capped_linear", LMHead)              # y W^T, tied to the embedding's table or not, then an optional cap
 

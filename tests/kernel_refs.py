@@ -354,7 +354,8 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G,
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
-                   block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None, window=0):
+                   block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None, window=0, cap=0.0,
+                   sink_values=None, mix_after=False, values_in_keys=False, stats=None):
     T = q_rows.shape[0]
     rep = H // G
     for t in range(T):
@@ -368,13 +369,18 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         js = list(range(first, pos + 1))
         pages = [int(page_table[slot, j // PAGE]) for j in js]
         k = torch.stack([kpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, d]
-        v = torch.stack([vpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, dv]
+        v = k[..., :dv] if values_in_keys else torch.stack([vpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()
         q = q_rows[t, :H * d].view(H, d).double()
         raw = torch.einsum("hd,nhd->hn", q, k.repeat_interleave(rep, dim=1)) * scale
-        s = talk.double() @ raw if talk is not None else raw
-        m = torch.clamp(s.max(dim=1, keepdim=True).values, min=0.0)
+        if cap:
+            raw = cap * torch.tanh(raw / cap)
+        s = talk.double() @ raw if talk is not None and not mix_after else raw
+        z = sink_values.double()[:, None] if sink_values is not None else torch.zeros(H, 1, dtype=torch.float64)
+        m = torch.maximum(s.max(dim=1, keepdim=True).values, z)
         e = torch.exp(s - m)
-        p = e / ((torch.exp(-m) if sink else 0.0) + e.sum(dim=1, keepdim=True))
+        p = e / ((torch.exp(z - m) if sink else 0.0) + e.sum(dim=1, keepdim=True))
+        if talk is not None and mix_after:
+            p = talk.double() @ p
         o = torch.einsum("hn,nhv->hv", p, v.repeat_interleave(rep, dim=1))
         if inv_v is not None:
             o = _turn(o, pos, inv_v, sign=-1.0)
@@ -384,6 +390,10 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
 
 def talk_attention_scratch_floats(T, n_chunks, H, dv):
     return T * n_chunks * H * (dv + 2) if n_chunks > 1 else 0
+
+
+def talk_attention_stats_floats(T, H):
+    return 2 * T * H
 
 
 def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, H,
@@ -431,9 +441,9 @@ def dyt_norm(h, res, alpha, weight, bias, out, rows=None):
 
 
 def causal_conv_silu(rows, col_off, channels, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start, seq_end,
-                     n_seq, out, one_token=False):
+                     n_seq, out, one_token=False, act=True):
     taps = weight.shape[1]
-    w, b = weight.double(), bias.double()
+    w, b = weight.double(), bias.double() if bias is not None else torch.zeros(channels, dtype=torch.float64)
     for s in range(n_seq):
         slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
         if n <= 0:
@@ -444,7 +454,7 @@ def causal_conv_silu(rows, col_off, channels, weight, bias, state, tok_seq, seq_
         acc = b.expand(n, channels).clone()
         for j in range(taps):
             acc += w[:, taps - 1 - j] * full[taps - 1 - j:taps - 1 - j + n]
-        out[row0:row0 + n] = (acc * torch.sigmoid(acc)).to(out.dtype)
+        out[row0:row0 + n] = (acc * torch.sigmoid(acc) if act else acc).to(out.dtype)
         if slot >= 0 and taps > 1:
             state[slot, :taps - 1] = full[n:n + taps - 1].float()
     return out
@@ -498,10 +508,113 @@ def rmsnorm_accumulate(x, weight, eps, scale, acc, first=False):
     return acc
 
 
-def sigmoid_gate(x, rows, g_off):
-    g = rows[:, g_off:g_off + x.shape[1]].double()
+def sigmoid_gate(x, rows, g_off, per=1):
+    g = rows[:, g_off:g_off + x.shape[1] // per].double().repeat_interleave(per, dim=1)
     x.copy_((x.double() * torch.sigmoid(g)).to(x.dtype))
     return x
+
+
+# ---------------------------------------------------------------------------
+# the norm in groups after a scaled residual sum; filtered, normed and compressed attention inputs; products per head
+# ---------------------------------------------------------------------------
+
+def group_norm(h, res, alpha, weight, eps, groups, out, rows=None):
+    def normed(v):
+        R, H = v.shape
+        g = v.view(R, groups, H // groups)
+        g = g / torch.sqrt((g * g).mean(-1, keepdim=True) + eps)
+        return g.reshape(R, H) * weight.double()
+    if res is not None:
+        v = normed(float(np.float32(alpha)) * h.double() + res.double())
+        h.copy_(v.float())
+        if out is not None:
+            out.copy_(h.to(out.dtype))
+        return out
+    src = h if rows is None else h[rows.long()]
+    out.copy_(normed(src.double()).to(out.dtype))
+    return out
+
+
+def round_rows(h, out):
+    out.copy_(h.to(out.dtype))
+    return out
+
+
+def qkv_conv_norm_store(rows, H, G, d, dv, conv_w, conv_state, wq, wk, v_unit, eps, tok_pos, tok_seq, seq_slot,
+                        seq_first_row, seq_start, seq_end, n_seq, q_out, kpool, vpool, page_table, one_token=False):
+    C = H * d + G * (d + dv)
+    taps = conv_w.shape[1] if conv_w is not None else 0
+    for s in range(n_seq):
+        slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
+        if n <= 0:
+            continue
+        x = rows[row0:row0 + n, :C].double()
+        if taps > 1:
+            past = conv_state[slot].double() if slot >= 0 else torch.zeros(taps - 1, C, dtype=torch.float64)
+            full = torch.cat([past, x], dim=0)
+            y = torch.zeros(n, C, dtype=torch.float64)
+            for j in range(taps):
+                y += conv_w.double()[:, taps - 1 - j] * full[taps - 1 - j:taps - 1 - j + n]
+            if slot >= 0:
+                conv_state[slot] = full[n:n + taps - 1].float()
+        elif taps == 1:
+            y = x * conv_w.double()[:, 0]
+        else:
+            y = x
+        q, k, v = y[:, :H * d], y[:, H * d:H * d + G * d], y[:, H * d + G * d:].reshape(n, G, dv)
+        if wq is not None:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * wq.double()
+        if wk is not None:
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * wk.double()
+        if v_unit:
+            v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        q_out[row0:row0 + n] = q.to(q_out.dtype)
+        if slot < 0:
+            continue
+        for i in range(n):
+            pos = int(tok_pos[row0 + i])
+            page = int(page_table[slot, pos // PAGE])
+            kpool[page, :, pos % PAGE] = k[i].view(G, d).to(kpool.dtype)
+            vpool[page, :, pos % PAGE] = v[i].to(vpool.dtype)
+    return q_out
+
+
+def latent_rotate_store(rows, lat_off, H, d, dr, R, wc, eps, inv_freq, amp, tok_pos, tok_seq, seq_slot, qfull, kpool,
+                        page_table, rot=None):
+    T = rows.shape[0]
+    D = R + dr
+    for t in range(T):
+        pos, slot = int(tok_pos[t]), int(seq_slot[int(tok_seq[t])])
+        ang = float(np.float32(pos)) * inv_freq.double()
+        cs, sn = torch.cos(ang) * float(np.float32(amp)), torch.sin(ang) * float(np.float32(amp))
+        if rot is not None:                   # pairs from rot / 2 on pass as they are
+            cs[rot // 2:], sn[rot // 2:] = 1.0, 0.0
+
+        def turn(x):
+            a, b = x[..., 0::2], x[..., 1::2]
+            out = torch.empty_like(x)
+            out[..., 0::2] = a * cs - b * sn
+            out[..., 1::2] = b * cs + a * sn
+            return out
+        row = rows[t].double()
+        q = row[:H * (d + dr)].view(H, d + dr)
+        qfull.view(T, H, D)[t, :, R:] = turn(q[:, d:]).to(qfull.dtype)
+        if slot < 0:
+            continue
+        lat = row[lat_off:lat_off + D]
+        c = lat[:R] / torch.sqrt((lat[:R] * lat[:R]).mean() + eps) * wc.double()
+        page = int(page_table[slot, pos // PAGE])
+        kpool[page, 0, pos % PAGE, :R] = c.to(kpool.dtype)
+        kpool[page, 0, pos % PAGE, R:] = turn(lat[R:]).to(kpool.dtype)
+    return qfull
+
+
+def head_linear(x, x_head, x_off, w, out, o_head, o_off):
+    Hn, O, I = w.shape
+    for h in range(Hn):
+        xi = x[:, h * x_head + x_off:h * x_head + x_off + I].double()
+        out[:, h * o_head + o_off:h * o_head + o_off + O] = (xi @ w[h].double().T).to(out.dtype)
+    return out
 
 
 def moe_route(z, correction, n_experts, group_count, group_keep, top, scale, shared_gate, out):
