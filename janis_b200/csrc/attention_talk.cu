@@ -331,10 +331,13 @@ struct TalkMmaShape {
     int hg;             // groups the heads are cut into: a CTA forms the scores of all heads and the weights and sums of
                         // its own group (1: all heads in one CTA; more where all heads' sums do not fit shared memory)
     float scale;
+    float cap;          // > 0: raw <- cap tanh(raw / cap)
+    int mode;           // as TalkShape::mode: 0 one pass; 1 maxima and denominators only; 2 final weights mixed after the softmax
+    int v_in_keys;      // the values are the first dv features of the keys: the tile of keys serves as the tile of values
 };
 
 struct TalkMmaLayout {
-    size_t q, kv, raw, p, o, m, l, corr, talk, meta, total;
+    size_t q, kv, raw, p, o, m, l, corr, talk, fin, meta, total;
     int qs, kvs, rs, ps, os;       // row strides in elements
 };
 
@@ -352,6 +355,7 @@ __host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, in
     L.l = at;    at += (size_t)hp * qr * 4;
     L.corr = at; at += (size_t)hp * qr * 4;
     L.talk = at; at += (size_t)H * H * 4;
+    L.fin = at;  at += (size_t)2 * H * qr * 4;          // mode 2: every (head, row)'s final maximum and 1 / denominator
     L.meta = at; at += (3 * 16 + 64) * 4;
     L.total = at;
     return L;
@@ -364,7 +368,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                           const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
                           const int* __restrict__ page_table, int table_stride, const float* __restrict__ talk,
                           const float* __restrict__ inv_v, bf16* __restrict__ out, float* __restrict__ partial,
-                          int n_tok, TalkMmaShape sh) {
+                          const float* __restrict__ sink_vals, float* __restrict__ stats, int n_tok, TalkMmaShape sh) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = sh.H, G = sh.G, d = sh.d, dv = sh.dv, QR = sh.qr, BN = sh.bn, rep = H / G;
     const int HP = H / sh.hg, h0 = ((int)blockIdx.y % sh.hg) * HP;       // this CTA's heads: h0 .. h0 + HP - 1
@@ -378,6 +382,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     float* l_s = reinterpret_cast<float*>(smem_raw + L.l);
     float* corr_s = reinterpret_cast<float*>(smem_raw + L.corr);
     float* talk_s = reinterpret_cast<float*>(smem_raw + L.talk);
+    float* fm_s = reinterpret_cast<float*>(smem_raw + L.fin);
+    float* fl_s = fm_s + (size_t)H * QR;
     int* pos_s = reinterpret_cast<int*>(smem_raw + L.meta);
     int* seq_s = pos_s + 16;
     int* slot_s = pos_s + 32;
@@ -399,10 +405,24 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         for (int u = tid; u < H * H; u += TALK_MMA_THREADS) talk_s[u] = talk[u];
     for (int u = tid; u < HP * QR * L.os; u += TALK_MMA_THREADS) o_s[u] = 0.f;
     for (int u = tid; u < HP * QR; u += TALK_MMA_THREADS) {
-        m_s[u] = sh.sink && !split ? 0.f : -CUDART_INF_F;
-        l_s[u] = sh.sink && !split ? 1.f : 0.f;
+        const bool with_sink = sh.sink && !split && sh.mode != 2;
+        m_s[u] = with_sink ? (sink_vals != nullptr ? sink_vals[h0 + u / QR] : 0.f) : -CUDART_INF_F;
+        l_s[u] = with_sink || sh.mode == 2 ? 1.f : 0.f;      // (mode 2: the weights arrive normalised)
+        corr_s[u] = 1.f;
     }
     grid_dependency_wait();
+    if (sh.mode == 2)
+        for (int u = tid; u < H * QR; u += TALK_MMA_THREADS) {
+            const int h = u / QR, r = u & (QR - 1);
+            float M = 0.f, inv = 0.f;
+            if (r < n_rows) {
+                const float Lr = stats[(size_t)(r0 + r) * 2 * H + 2 * h + 1];
+                M = stats[(size_t)(r0 + r) * 2 * H + 2 * h];
+                inv = Lr > 0.f ? 1.f / Lr : 0.f;
+            }
+            fm_s[u] = M;
+            fl_s[u] = inv;
+        }
     // queries: a warp per (head, row), a lane per 16 bytes; rows beyond the step's end are zero
     for (int hr = warp; hr < H * QR; hr += TALK_MMA_WARPS) {
         const int h = hr / QR, r = hr & (QR - 1);
@@ -476,11 +496,16 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                             if (t < n_here) {
                                 if (r >= QR) continue;        // (one row kept: the other rows of the operand repeat it)
                                 float* dst = raw_s + ((size_t)g * QR + r) * L.rs + (nt0 + t) * 8 + (lane & 3) * 2;
-                                dst[0] = acc[t][0] * sh.scale;
-                                dst[1] = acc[t][1] * sh.scale;
+                                float z[4] = {acc[t][0] * sh.scale, acc[t][1] * sh.scale, acc[t][2] * sh.scale, acc[t][3] * sh.scale};
+                                if (sh.cap > 0.f) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) z[e] = sh.cap * tanhf(z[e] / sh.cap);
+                                }
+                                dst[0] = z[0];
+                                dst[1] = z[1];
                                 if (QR == 16) {
-                                    dst[8 * L.rs] = acc[t][2] * sh.scale;
-                                    dst[8 * L.rs + 1] = acc[t][3] * sh.scale;
+                                    dst[8 * L.rs] = z[2];
+                                    dst[8 * L.rs + 1] = z[3];
                                 }
                             }
                     }
@@ -494,9 +519,30 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     if (seen && sh.window > 0) seen = j > pos_s[r] - sh.window;
                     float* at = raw_s + (size_t)r * L.rs + c;
                     const size_t hs = (size_t)QR * L.rs;
-                    if (!seen) {
+                    if (sh.mode == 2) {
+                        // every head's final weight of this key, mixed over the heads; P is written here
+                        float w[HMAX];
+#pragma unroll
+                        for (int g = 0; g < HMAX; ++g)
+                            w[g] = g < H && seen ? expf(at[g * hs] - fm_s[g * QR + r]) * fl_s[g * QR + r] : 0.f;
+                        for (int h = h0; h < h0 + HP; ++h) {
+                            float s = w[0];
+                            if (talk != nullptr) {
+                                const float* tr = talk_s + h * H;
+                                s = 0.f;
+#pragma unroll
+                                for (int g = 0; g < HMAX; ++g)
+                                    if (g < H) s = fmaf(tr[g], w[g], s);
+                            } else {
+#pragma unroll
+                                for (int g = 0; g < HMAX; ++g)
+                                    if (g == h) s = w[g];
+                            }
+                            p_s[((size_t)(h - h0) * QR + r) * L.ps + c] = __float2bfloat16_rn(s);
+                        }
+                    } else if (!seen) {
                         for (int h = h0; h < h0 + HP; ++h) at[h * hs] = -CUDART_INF_F;
-                    } else if (talk != nullptr) {
+                    } else if (talk != nullptr && sh.mode == 0) {
                         float raw[HMAX];
 #pragma unroll
                         for (int g = 0; g < HMAX; ++g) raw[g] = g < H ? at[g * hs] : 0.f;
@@ -512,7 +558,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- 2b: online softmax of every (head, row); P as bfloat16
-                for (int u = warp; u < HP * QR; u += TALK_MMA_WARPS) {
+                for (int u = warp; u < HP * QR && sh.mode != 2; u += TALK_MMA_WARPS) {
                     const float* src = raw_s + ((size_t)h0 * QR + u) * L.rs;
                     const float s0 = lane < BN ? src[lane] : -CUDART_INF_F;
                     const float s1 = lane + 32 < BN ? src[lane + 32] : -CUDART_INF_F;
@@ -536,8 +582,9 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     if (lane + 32 < BN) dst[lane + 32] = __float2bfloat16_rn(p1);
                 }
                 __syncthreads();
-                // ---- values of the tile, into the keys' place
-                for (int row = warp; row < G * BN; row += TALK_MMA_WARPS) {
+                if (sh.mode == 1) continue;                  // (the barrier at the top of the next tile's load orders the reuse)
+                // ---- values of the tile, into the keys' place (values that lie in the keys are there already)
+                for (int row = warp; row < G * BN && !sh.v_in_keys; row += TALK_MMA_WARPS) {
                     const int g = row >> bn_log2, jj = row & (BN - 1), at = base_s[jj];
                     bf16* dst = kv_s + (size_t)row * L.kvs;
                     const bf16* src = vpool + ((size_t)(at < 0 ? 0 : at) + (size_t)g * JANIS_PAGE) * dv;
@@ -602,12 +649,30 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         a = b;
     }
     __syncthreads();
+    if (sh.mode == 1 && !split) {
+        // every (row, head)'s maximum and denominator, for the pass that forms the weights
+        for (int u = tid; u < n_rows * HP; u += TALK_MMA_THREADS) {
+            const int h = u % HP, r = u / HP;
+            const bool live = slot_s[r] >= 0;
+            float* dst = stats + (size_t)(r0 + r) * 2 * H + 2 * (h0 + h);
+            dst[0] = live ? m_s[h * QR + r] : 0.f;
+            dst[1] = live ? l_s[h * QR + r] : 0.f;
+        }
+        return;
+    }
     if (split) {
-        // the chunk's share of row r0: per head the unnormalised sums, then the maximum and the denominator
-        float* dst = partial + ((size_t)r0 * (gridDim.y / sh.hg) + blockIdx.y / sh.hg) * H * (dv + 2) + (size_t)h0 * (dv + 2);
+        // the chunk's share of row r0: per head the unnormalised sums, then the maximum and the denominator.  (Weights
+        // that are final already, mode 2, add up as they are: maximum 0, and the first chunk alone brings the 1 that
+        // the sums are divided by.)
+        const int chunk_id = (int)blockIdx.y / sh.hg;
+        float* dst = partial + ((size_t)r0 * (gridDim.y / sh.hg) + chunk_id) * H * (dv + 2) + (size_t)h0 * (dv + 2);
         for (int u = tid; u < HP * (dv + 2); u += TALK_MMA_THREADS) {
             const int h = u / (dv + 2), c = u % (dv + 2);
-            dst[u] = c < dv ? o_s[(size_t)h * QR * L.os + c] : (c == dv ? m_s[h * QR] : l_s[h * QR]);
+            float x;
+            if (c < dv) x = sh.mode == 1 ? 0.f : o_s[(size_t)h * QR * L.os + c];
+            else if (sh.mode == 2) x = c == dv ? 0.f : (chunk_id == 0 ? 1.f : 0.f);
+            else x = c == dv ? m_s[h * QR] : l_s[h * QR];
+            dst[u] = x;
         }
         return;
     }
@@ -639,7 +704,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
 __global__ void __launch_bounds__(128)
 talk_attention_merge_kernel(const float* __restrict__ partial, int n_chunks, const int* __restrict__ tok_pos,
                             const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
-                            const float* __restrict__ inv_v, bf16* __restrict__ out, int H, int dv, int sink) {
+                            const float* __restrict__ inv_v, bf16* __restrict__ out, int H, int dv, int sink,
+                            const float* __restrict__ sink_vals) {
     const int t = blockIdx.x, tid = threadIdx.x;
     grid_dependents_launch();
     const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
@@ -652,9 +718,10 @@ talk_attention_merge_kernel(const float* __restrict__ partial, int n_chunks, con
         if (slot >= 0) {
             const float* ph = base + (size_t)h * (dv + 2);
             const size_t cs = (size_t)H * (dv + 2);
-            float M = sink ? 0.f : -CUDART_INF_F;
+            const float z = sink_vals != nullptr ? sink_vals[h] : 0.f;
+            float M = sink ? z : -CUDART_INF_F;
             for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ph[c * cs + dv]);
-            float Lsum = sink ? expf(-M) : 0.f, a0 = 0.f, a1 = 0.f;
+            float Lsum = sink ? expf(z - M) : 0.f, a0 = 0.f, a1 = 0.f;
             for (int c = 0; c < n_chunks; ++c) {
                 const float mc = ph[c * cs + dv];
                 if (mc == -CUDART_INF_F) continue;
@@ -676,6 +743,35 @@ talk_attention_merge_kernel(const float* __restrict__ partial, int n_chunks, con
         bf16* o_row = out + (size_t)t * H * dv + (size_t)h * dv;
         o_row[m] = __float2bfloat16_rn(lo);
         o_row[m + hv] = __float2bfloat16_rn(hi);
+    }
+}
+
+// The chunks' maxima and denominators of a decode row put together into the row's own (`stats`), per head.
+__global__ void __launch_bounds__(64)
+talk_attention_stats_merge_kernel(const float* __restrict__ partial, int n_chunks, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ seq_slot, float* __restrict__ stats, int H, int dv, int sink,
+                                  const float* __restrict__ sink_vals) {
+    const int t = blockIdx.x;
+    grid_dependents_launch();
+    const int slot = seq_slot[tok_seq[t]];
+    grid_dependency_wait();
+    const float* base = partial + (size_t)t * n_chunks * H * (dv + 2);
+    const size_t cs = (size_t)H * (dv + 2);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float M = 0.f, Lsum = 0.f;
+        if (slot >= 0) {
+            const float* ph = base + (size_t)h * (dv + 2);
+            const float z = sink_vals != nullptr ? sink_vals[h] : 0.f;
+            M = sink ? z : -CUDART_INF_F;
+            for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ph[c * cs + dv]);
+            Lsum = sink ? expf(z - M) : 0.f;
+            for (int c = 0; c < n_chunks; ++c) {
+                const float mc = ph[c * cs + dv];
+                if (mc != -CUDART_INF_F) Lsum = fmaf(expf(mc - M), ph[c * cs + dv + 1], Lsum);
+            }
+        }
+        stats[(size_t)t * 2 * H + 2 * h] = M;
+        stats[(size_t)t * 2 * H + 2 * h + 1] = Lsum;
     }
 }
 
@@ -758,7 +854,8 @@ template <int HMAX>
 static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_pos, const int* tok_seq, const int* seq_slot,
                            const void* kpool, const void* vpool, const int* page_table, int table_stride,
                            const float* talk, const float* inv_v, void* out, float* partial, int n_chunks, int T,
-                           const TalkMmaShape& sh, size_t bytes, cudaStream_t stream) {
+                           TalkMmaShape sh, size_t bytes, cudaStream_t stream, const float* sink_vals, float* stats,
+                           bool two_pass) {
     static size_t most = 0;
     if (bytes > most) {
         cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<HMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -766,13 +863,25 @@ static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_p
         most = bytes;
     }
     const dim3 grid((T + sh.rows - 1) / sh.rows, (sh.chunk > 0 ? n_chunks : 1) * sh.hg), block(TALK_MMA_THREADS);
-    if (launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
-                      q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
-                      table_stride, talk, inv_v, (bf16*)out, partial, T, sh))
-        return 1;
-    if (sh.chunk == 0) return 0;
-    return launch_kernel("talk_attention_merge", talk_attention_merge_kernel, dim3(T), dim3(128), 0, stream, 1,
-                         (const float*)partial, n_chunks, tok_pos, tok_seq, seq_slot, inv_v, (bf16*)out, sh.H, sh.dv, sh.sink);
+    // heads mixed after the softmax: a pass for the rows' maxima and denominators, then the pass of the weights
+    for (int pass = two_pass ? 1 : 0; pass <= (two_pass ? 2 : 0); ++pass) {
+        sh.mode = pass;
+        if (launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
+                          q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
+                          table_stride, talk, inv_v, (bf16*)out, partial, sink_vals, stats, T, sh))
+            return 1;
+        if (sh.chunk == 0) continue;
+        if (pass == 1) {
+            if (launch_kernel("talk_attention_stats_merge", talk_attention_stats_merge_kernel, dim3(T), dim3(64), 0, stream, 1,
+                              (const float*)partial, n_chunks, tok_seq, seq_slot, stats, sh.H, sh.dv, sh.sink, sink_vals))
+                return 1;
+        } else if (launch_kernel("talk_attention_merge", talk_attention_merge_kernel, dim3(T), dim3(128), 0, stream, 1,
+                                 (const float*)partial, n_chunks, tok_pos, tok_seq, seq_slot, inv_v, (bf16*)out, sh.H, sh.dv,
+                                 pass == 2 ? 0 : sh.sink, sink_vals)) {
+            return 1;
+        }
+    }
+    return 0;
 }
 
 JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_elems, const int* tok_pos,
@@ -795,13 +904,13 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     if (two_pass && (stats == nullptr || stats_floats < (long long)T * 2 * H))
         return fail("talk_attention: heads mixed after the softmax need %lld floats for the rows' maxima and denominators", (long long)T * 2 * H);
     if (v_in_keys) vpool = kpool;
-    const bool mma_takes = cap == 0.f && sink_vals == nullptr && !two_pass && !v_in_keys;
-    if (mma_takes && dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
+    if (dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
         (((uintptr_t)q_rows | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0) {
         size_t mma_bytes = 0;
         TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
         if (ms.qr) {
             ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale; ms.window = window;
+            ms.cap = cap; ms.mode = 0; ms.v_in_keys = v_in_keys ? 1 : 0;
             if (one_row && n_chunks > 1 && max_keys > 0 && partial != nullptr) {
                 // a decode row's keys over n_chunks CTAs, each a whole number of tiles
                 if (partial_floats < (long long)T * n_chunks * H * (dv + 2))
@@ -811,12 +920,12 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
             }
             if (H <= 8)
                 return talk_mma_launch<8>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                          talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
+                                          talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream, sink_vals, stats, two_pass);
             if (H <= 16)
                 return talk_mma_launch<16>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                           talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
+                                           talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream, sink_vals, stats, two_pass);
             return talk_mma_launch<32>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                       talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
+                                       talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream, sink_vals, stats, two_pass);
         }
     }
     size_t bytes = 0;
