@@ -523,10 +523,35 @@ def nosolix_like(gemma: dict, layers: int) -> dict:
             "norm": {"eps": 1e-6}, "layers": out}
 
 
+def vivazen_like(gemma: dict, layers: int) -> dict:
+    """A Vivazen configuration with the layer sizes of a Gemma2 one: the same width, heads, head size (for keys and
+    values), feed-forward width and vocabulary; layers alternate "attention" (Gemma2's heads and key/value heads, a
+    filter of 4 taps, scores capped at 30, no window) and "latent_attention" (as many heads, each half the head size
+    plain and a quarter rotated, values of half the head size, a compressed row as wide as one head, Gemma2's
+    window); the last layer of every four runs the tensors of the one two before it."""
+    hd, W, ff = int(gemma["head_dim"]), int(gemma["hidden_size"]), int(gemma["intermediate_size"])
+    att = {"heads": gemma["num_attention_heads"], "kv_heads": gemma["num_key_value_heads"], "dim": hd, "vdim": hd,
+           "scale": hd ** -0.5, "softcap": 30.0, "conv": 4}
+    lat = {"heads": gemma["num_attention_heads"], "dim": hd // 2, "rot_dim": hd // 4, "vdim": hd // 2, "kv_rank": hd,
+           "scale": (hd // 2 + hd // 4) ** -0.5, "mask": {"size": int(gemma.get("sliding_window", 4096))},
+           "rot": {"base": 10000.0, "dims": hd // 4, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": ff}
+    out = []
+    for i in range(layers):
+        entry = {"type": "latent_attention" if i % 2 else "attention", "mixer": copy.deepcopy(lat if i % 2 else att), "mlp": dict(mlp)}
+        if i % 4 == 3:
+            entry["weights_of"] = i - 2
+        out.append(entry)
+    return {"architecture": "Vivazen", "vocab": gemma["vocab_size"], "width": W, "norm": {"eps": 1e-6, "groups": 8},
+            "postln_alpha": 2.0, "layers": out}
+
+
 _TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_norm_gate", "bias_act", "add_rmsnorm", "rmsnorm"),
           "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act"),
           "nosolix": ("talk_attention", "qkv_rotate_store", "selective_scan", "causal_conv_silu", "gate_group_norm",
-                      "moe_route", "moe_expert_act", "dyt_norm", "rmsnorm_accumulate", "sigmoid_gate", "bias_act")}
+                      "moe_route", "moe_expert_act", "dyt_norm", "rmsnorm_accumulate", "sigmoid_gate", "bias_act"),
+          "vivazen": ("talk_attention", "qkv_conv_norm_store", "latent_rotate_store", "head_linear", "group_norm", "round_rows",
+                      "sigmoid_gate", "gated_act")}
 
 
 def _leaf_mixers(mixer):
@@ -602,7 +627,7 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
     # the elementwise kernels of a step against the bytes of the residual stream they pass over (one float32 read and
     # write and one activation written per norm): the norms' share, a number to set beside the other design's
     T = prefill_tokens
-    for nm in ("dyt_norm", "add_rmsnorm"):
+    for nm in ("dyt_norm", "add_rmsnorm", "group_norm"):
         if kernels["prefill_us"].get(nm):
             n_norm = sum(2 if getattr(model.blocks[c.layer], "feed_forward", None) is not None else 1 for c in model.schedule)
             roof[f"{nm}_prefill_frac_of_copy_bandwidth"] = round(n_norm * T * model.hidden * 10 / (kernels["prefill_us"][nm] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
@@ -618,11 +643,16 @@ def compare(sizes=("gemma2-2b", "gemma2-9b", "gemma2-27b"), layers: int = 4, pre
     weights: prompt tokens a second, decode tokens a second, and the device time of each design's own kernels in
     one prompt step and one decode step with what fraction of the roofline that is."""
     pk, pk_kind = peaks()
-    rec = {"compare": f"{design} beside {'sigalorn' if design == 'nosolix' else 'gemma2'}", "dtype": "bf16", "data": "synthetic",
+    rec = {"compare": f"{design} beside {'sigalorn' if design in ('nosolix', 'vivazen') else 'gemma2'}", "dtype": "bf16", "data": "synthetic",
            "peaks": pk_kind, "prefill_tokens": prefill_tokens, "batch": batch, "context": context, "steps": steps, "sizes": {}}
     for name in sizes:
         gemma = dict(load_config(name), num_hidden_layers=layers)
         gemma.pop("layer_types", None)
+        if design == "vivazen":      # beside the design whose attention runs through the same kernel
+            rec["sizes"][name] = {
+                "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup),
+                "vivazen": _measure_design(vivazen_like(gemma, layers), "vivazen", pk, prefill_tokens, batch, context, steps, warmup)}
+            continue
         if design == "nosolix":      # beside the closest design the library has: recurrent layers between attention over a limited span
             rec["sizes"][name] = {
                 "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup),
@@ -655,8 +685,8 @@ def main(argv=None) -> int:
                     "instead of sequences that all reach --context")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
-    ap.add_argument("--compare", choices=["sigalorn", "nosolix"], default="",
-                    help="instead of the benchmark: Sigalorn beside Gemma2, or Nosolix beside Sigalorn, at equal layer "
+    ap.add_argument("--compare", choices=["sigalorn", "nosolix", "vivazen"], default="",
+                    help="instead of the benchmark: Sigalorn beside Gemma2, or Nosolix or Vivazen beside Sigalorn, at equal layer "
                     "sizes (prompt and decode throughput, and each design's own kernels against their rooflines); "
                     "--config picks one size")
     a = ap.parse_args(argv)

@@ -469,10 +469,13 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 {
                     const int nts = BN / 8;
                     int tg = 4;                               // tiles a unit: fewer where the warps would outnumber the units
-                    while (tg > 1 && H * ((nts + tg - 1) / tg) < TALK_MMA_WARPS) tg >>= 1;
+                    while (tg > 1 && (talk == nullptr || sh.mode == 1 ? HP : H) * ((nts + tg - 1) / tg) < TALK_MMA_WARPS) tg >>= 1;
                     const int groups = (nts + tg - 1) / tg;
-                    for (int unit = warp; unit < H * groups; unit += TALK_MMA_WARPS) {
-                        const int g = unit / groups, nt0 = (unit % groups) * tg, n_here = min(tg, nts - nt0), kvh = g / rep;
+                    // (where nothing mixes the heads' scores, a CTA forms those of its own heads alone)
+                    const bool own_only = talk == nullptr || sh.mode == 1;
+                    const int g_first = own_only ? h0 : 0, g_count = own_only ? HP : H;
+                    for (int unit = warp; unit < g_count * groups; unit += TALK_MMA_WARPS) {
+                        const int g = g_first + unit / groups, nt0 = (unit % groups) * tg, n_here = min(tg, nts - nt0), kvh = g / rep;
                         float acc[4][4];
 #pragma unroll
                         for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;

@@ -31,13 +31,13 @@ class GatedMLP(FeedForward):
                  init_std: float = 0.02):
         if act not in _ACTS:
             raise ValueError(f"unknown activation {act!r} (known: {sorted(_ACTS)})")
-        if intermediate % self.GROUP:
-            raise ValueError(f"the fused gate/up layout needs an intermediate width that is a multiple of "
-                             f"{self.GROUP}, found {intermediate}")
         for k in ("gate", "up", "down"):
             if k not in names:
                 raise ValueError(f"feed-forward needs the checkpoint name of its {k!r} projection")
         self.hidden, self.intermediate = hidden, intermediate
+        # the fused gate/up layout wants whole groups: an intermediate width that is no multiple of the group is
+        # padded with zero rows of gate and up (act(0) * 0 = 0) and zero columns of down
+        self.padded = -(-intermediate // self.GROUP) * self.GROUP
         self.act = _ACTS[act]
         self.names = dict(names)
         self.init_std = init_std
@@ -51,23 +51,27 @@ class GatedMLP(FeedForward):
                 self.names["down"]: TensorSpec((H, I), init_std=s)}
 
     def load(self, store, rt: Runtime):
-        if rt.dtype == torch.bfloat16 and self.hidden % 8:
-            raise ValueError(f"the bfloat16 products need a hidden width that is a multiple of 8, found {self.hidden}")
         g = store.get(self.names["gate"], rt.dtype)
         u = store.get(self.names["up"], rt.dtype)
-        I, H, G = self.intermediate, self.hidden, self.GROUP
+        I, H, G = self.padded, self.hidden, self.GROUP
+        if I != self.intermediate:
+            pad = torch.zeros(I - self.intermediate, H, dtype=g.dtype, device=g.device)
+            g, u = torch.cat([g, pad]), torch.cat([u, pad])
         fused = torch.stack([g.view(I // G, G, H), u.view(I // G, G, H)], dim=1)   # [I/G, 2, G, H]
         self.w_gu = fused.reshape(2 * I, H).contiguous()
         del g, u, fused
         store.drop(self.names["gate"], self.names["up"])                   # the fused copy is the one that stays
         self.w_down = store.get(self.names["down"], rt.dtype).contiguous()
+        if I != self.intermediate:
+            self.w_down = torch.cat([self.w_down, torch.zeros(H, I - self.intermediate, dtype=self.w_down.dtype,
+                                                              device=self.w_down.device)], dim=1).contiguous()
 
     def forward(self, x, ctx: StepContext):
         rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
-        T, I = ctx.n_tok, self.intermediate
+        T, I = ctx.n_tok, self.padded
         a = ws.buf("ffn.act", (T, I), rt.dtype)
         epi = ops.EPI_GATED_GELU if self.act == 0 else ops.EPI_GATED_SILU
-        if rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS:
+        if rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS and self.hidden % 8 == 0:   # (the skinny product reads 16 bytes at a time)
             ops.gemv_bf16(x, self.w_gu, a, epi)
         else:
             # (ops.gemm_tc05 computes this product with the activation fused for 17..64 rows, but at these

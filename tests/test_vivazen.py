@@ -98,18 +98,22 @@ VIV_C = _model(512, 128, 8, 1e-6, 3.5, [
     _layer("attention", _att(16, 16, 16, 32, 0.25, conv=4), None),
     BORROW(0)])
 
-# sizes that are multiples of little; a window of five and a window of one position; a rotated part of two features
+# sizes that are multiples of little (a feed-forward width of 21); a window of five and a window of one position; a
+# rotated part of two features
 VIV_D = _model(301, 72, 3, 1e-4, 1.7, [
     _layer("attention", _att(5, 5, 10, 6, 0.3, conv=5, cap=3.0), 40),
-    _layer("latent_attention", _lat(3, 12, 6, 14, 10, 0.3, window=5, base=100.0), 24),
+    _layer("latent_attention", _lat(3, 12, 6, 14, 10, 0.3, window=5, base=100.0), 21),
     _layer("latent_attention", _lat(1, 6, 2, 6, 7, 0.4, window=1, base=100.0, scaling=(3.0, 16, 2.0, 1.0)), None),
     BORROW(0)])
 
 # each mixer alone, without a feed-forward
 VIV_E = _model(150, 48, 4, 1e-6, 1.0, [_layer("attention", _att(3, 1, 16, 16, 0.25, conv=4, cap=8.0), None)])
 VIV_F = _model(150, 48, 2, 1e-6, 1.0, [_layer("latent_attention", _lat(3, 8, 8, 16, 16, 0.25, window=9, scaling=(2.0, 16, 4.0, 1.0)), None)])
+# a width that is no multiple of 8
+VIV_G = _model(97, 36, 9, 1e-5, 2.5, [_layer("attention", _att(2, 1, 12, 12, 0.3, conv=2), 30),
+                                      _layer("latent_attention", _lat(2, 4, 4, 6, 12, 0.3, window=40), 18)])
 
-VIV = {"A": VIV_A, "B": VIV_B, "C": VIV_C, "D": VIV_D, "E": VIV_E, "F": VIV_F}
+VIV = {"A": VIV_A, "B": VIV_B, "C": VIV_C, "D": VIV_D, "E": VIV_E, "F": VIV_F, "G": VIV_G}
 
 
 def write_vivazen(model_dir: str, raw: dict, seed: int, gain: float = 4.0, norm_gain: float = 2.0, q_gain: float = 8.0,
@@ -179,7 +183,7 @@ def engines(viv_dirs):
 
 
 def keys_for(on):
-    return ["A", "B", "C", "D", "E", "F"] if on == "cuda" else ["A", "B", "D", "E", "F"]
+    return ["A", "B", "C", "D", "E", "F", "G"] if on == "cuda" else ["A", "B", "D", "E", "F", "G"]
 
 
 def _requests(vocab, lens, seed):
