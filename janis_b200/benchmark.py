@@ -570,7 +570,7 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
     eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=batch * max(context, prefill_tokens) + 64,
                                  max_batch=batch, max_context=max(context, prefill_tokens))
     ops, model = eng.rt.ops, eng.model
-    out = {"layers": len(model.blocks)}
+    out = {"layers": len(model.schedule)}
     pre = measure_prefill(eng, prefill_tokens, repeats=3, warmup=2)
     out["prefill_tok_s"] = round(pre["tok_s"], 1)
     out["prefill_ms"] = round(pre["ms"], 3)
@@ -631,6 +631,19 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
         if kernels["prefill_us"].get(nm):
             n_norm = sum(2 if getattr(model.blocks[c.layer], "feed_forward", None) is not None else 1 for c in model.schedule)
             roof[f"{nm}_prefill_frac_of_copy_bandwidth"] = round(n_norm * T * model.hidden * 10 / (kernels["prefill_us"][nm] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    # the kernels between an attention's projection and its scores (rotate or filter, norm, write the cache line): the
+    # projected rows read once and written once
+    for nm in ("qkv_rotate_store", "qkv_conv_norm_store"):
+        if kernels["prefill_us"].get(nm):
+            chans = 0
+            for call in model.schedule:
+                for mixer in _leaf_mixers(model.blocks[call.layer].mixer):
+                    if hasattr(mixer, "n_kv_heads") and any(isinstance(n, KVNeed) for n in mixer.cache_needs().values()):
+                        own = bool(getattr(mixer, "own_kv", True))
+                        chans += mixer.n_heads * mixer.key_dim + own * mixer.n_kv_heads * (mixer.key_dim + mixer.value_dim)
+            for mode, rows_n in (("prefill", T), ("decode", batch)):
+                if chans and kernels[f"{mode}_us"].get(nm):
+                    roof[f"{nm}_{mode}_frac_of_copy_bandwidth"] = round(rows_n * chans * 4 / (kernels[f"{mode}_us"][nm] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
     out["kernels"] = kernels
     out["kernel_rooflines"] = roof
     eng.close()

@@ -20,6 +20,7 @@
 namespace janis {
 
 constexpr int PREP_THREADS = 256;
+constexpr int PREP_MANY_ROWS = 1024;      // from here on a CTA of the wide kernel takes four rows
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
@@ -111,6 +112,190 @@ qkv_conv_norm_store_kernel(const T* __restrict__ rows, int row_elems, int H, int
     for (int c = tid; c < Cv; c += PREP_THREADS) {
         const int g = c / dv;
         vdst[(size_t)g * JANIS_PAGE * dv + c % dv] = from_float<T>(x_s[Cq + Ck + c] * inv_s[2 + g]);
+    }
+}
+
+// The same with 16 bytes a load and a store, for sizes that allow it (heads that are multiples of 16 bytes, up to four
+// taps known when the kernel is compiled).  A CTA takes TOK neighbouring rows of the step.  A thread keeps the filter of
+// its 16 bytes of channels in registers for all of them, and the step's last KT - 1 rows too, so a row is read once (and
+// KT - 1 rows before the CTA's first) and the filter once per CTA; where a tap reaches back before its sequence's part
+// of the step it takes the slot's kept input (or zero) instead.  The filtered rows wait in shared memory for the sums of
+// squares, which start in the filter's registers.  The sums' order depends on the sizes alone, not on TOK.
+// KT: the taps (1: no filter, or one tap that scales the channel).
+template <typename T, int KT, int TOK>
+__global__ void __launch_bounds__(PREP_THREADS)
+qkv_conv_norm_store_vec_kernel(const T* __restrict__ rows, int row_elems, int n_tok, int H, int G, int d, int dv,
+                               const float* __restrict__ conv_w, float* __restrict__ conv_state,
+                               const float* __restrict__ wq, const float* __restrict__ wk, int v_unit, float eps,
+                               const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                               const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                               const int* __restrict__ seq_start, const int* __restrict__ seq_end, T* __restrict__ q_out,
+                               T* __restrict__ kpool, T* __restrict__ vpool, const int* __restrict__ page_table,
+                               int table_stride) {
+    constexpr int V = Vec16<T>::N, NW = PREP_THREADS / 32, KB = KT > 1 ? KT - 1 : 1;
+    extern __shared__ float prep_smem[];
+    const int Cq = H * d, Ck = G * d, Cv = G * dv, C = Cq + Ck + Cv;
+    float* x_s = prep_smem;                         // TOK filtered rows
+    float* inv_s = x_s + (size_t)TOK * C;           // per row: 1 / rms of q, of k, of each value head
+    float* scratch = inv_s + TOK * (2 + G);         // per warp and row: the partial sums of q and of k
+    const int t0 = blockIdx.x * TOK, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_here = min(TOK, n_tok - t0);
+    grid_dependents_launch();
+    int in_seq[TOK], slot[TOK];
+    bool alone[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        in_seq[k] = 0, slot[k] = -1, alone[k] = false;
+        if (k < n_here) {
+            const int s = tok_seq[t0 + k];
+            slot[k] = seq_slot[s];
+            in_seq[k] = t0 + k - seq_first_row[s];
+            alone[k] = seq_end[s] - seq_start[s] == 1;      // the sequence's only token of the step shifts the kept inputs itself
+        }
+    }
+    grid_dependency_wait();
+    float sq[TOK], sk[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) sq[k] = sk[k] = 0.f;
+    for (int c0 = tid * V; c0 < C; c0 += PREP_THREADS * V) {
+        float w[V * KT], back[KB][V];                       // back[j - 1]: the step's row j before the one at hand
+        if (conv_w != nullptr) {
+#pragma unroll
+            for (int e = 0; e < V * KT; e += 4) Vec16<float>::load(conv_w + (size_t)c0 * KT + e, w + e);
+        }
+#pragma unroll
+        for (int j = 1; j < KT; ++j) {
+            if (t0 - j >= 0) {
+                Vec16<T>::load(rows + (size_t)(t0 - j) * row_elems + c0, back[j - 1]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) back[j - 1][e] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            if (k >= n_here) break;
+            float xs[KT][V], acc[V];
+            float* st = (KT > 1 && slot[k] >= 0) ? conv_state + (size_t)slot[k] * (KT - 1) * C : nullptr;
+            Vec16<T>::load(rows + (size_t)(t0 + k) * row_elems + c0, xs[0]);
+#pragma unroll
+            for (int j = 1; j < KT; ++j) {
+                const int idx = in_seq[k] - j;              // the input j tokens back
+                if (idx >= 0) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) xs[j][e] = back[j - 1][e];
+                } else if (st != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < V; e += 4) Vec16<float>::load(st + (size_t)(KT - 1 + idx) * C + c0 + e, xs[j] + e);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) xs[j][e] = 0.f;
+                }
+            }
+            if (conv_w != nullptr) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < KT; ++j) a = fmaf(w[e * KT + KT - 1 - j], xs[j][e], a);
+                    acc[e] = KT > 1 ? a : xs[0][e] * w[e];
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = xs[0][e];
+            }
+            if (KT > 1 && alone[k] && st != nullptr) {
+#pragma unroll
+                for (int j = 0; j < KT - 1; ++j)
+#pragma unroll
+                    for (int e = 0; e < V; e += 4) Vec16<float>::store(st + (size_t)(KT - 2 - j) * C + c0 + e, xs[j] + e);
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss = fmaf(acc[e], acc[e], ss);
+#pragma unroll
+            for (int e = 0; e < V; e += 4) Vec16<float>::store(x_s + (size_t)k * C + c0 + e, acc + e);
+            if (c0 < Cq) sq[k] += ss;
+            else if (c0 < Cq + Ck) sk[k] += ss;
+#pragma unroll
+            for (int j = KT - 2; j >= 1; --j)
+#pragma unroll
+                for (int e = 0; e < V; ++e) back[j][e] = back[j - 1][e];
+            if (KT > 1) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) back[0][e] = xs[0][e];
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        const float a = warp_sum(sq[k]), b = warp_sum(sk[k]);
+        if (lane == 0) scratch[(warp * TOK + k) * 2] = a, scratch[(warp * TOK + k) * 2 + 1] = b;
+    }
+    __syncthreads();                                        // (the filtered rows are whole now, too)
+    if (tid < 2 * TOK) {
+        const int k = tid >> 1, which = tid & 1;
+        float tot = 0.f;
+        for (int wp = 0; wp < NW; ++wp) tot += scratch[(wp * TOK + k) * 2 + which];
+        const float* wt = which ? wk : wq;
+        inv_s[k * (2 + G) + which] = wt != nullptr ? 1.f / sqrtf(tot / (float)(which ? Ck : Cq) + eps) : 1.f;
+    }
+    for (int p = warp; p < n_here * G; p += NW) {
+        const int k = p / G, g = p % G;
+        float sv = 0.f;
+        if (v_unit)
+            for (int c = lane; c < dv; c += 32) {
+                const float v = x_s[(size_t)k * C + Cq + Ck + g * dv + c];
+                sv = fmaf(v, v, sv);
+            }
+        sv = warp_sum(sv);
+        if (lane == 0) inv_s[k * (2 + G) + 2 + g] = v_unit ? 1.f / sqrtf(sv / (float)dv + eps) : 1.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        if (k >= n_here) break;
+        const float* xr = x_s + (size_t)k * C;
+        const float iq = inv_s[k * (2 + G)], ik = inv_s[k * (2 + G) + 1];
+        T* q_row = q_out + (size_t)(t0 + k) * Cq;
+        int page = 0;
+        const int pos = tok_pos[t0 + k];
+        if (slot[k] >= 0) page = page_table[(size_t)slot[k] * table_stride + pos / JANIS_PAGE];
+        T* kdst = kpool + ((size_t)page * G * JANIS_PAGE + pos % JANIS_PAGE) * d;
+        T* vdst = vpool + ((size_t)page * G * JANIS_PAGE + pos % JANIS_PAGE) * dv;
+        for (int c0 = tid * V; c0 < C; c0 += PREP_THREADS * V) {
+            float y[V], w[V];
+            T* dst;
+#pragma unroll
+            for (int e = 0; e < V; e += 4) Vec16<float>::load(xr + c0 + e, y + e);
+            if (c0 < Cq) {
+                dst = q_row + c0;
+                if (wq != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < V; e += 4) Vec16<float>::load(wq + c0 + e, w + e);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) y[e] = y[e] * iq * w[e];
+                }
+            } else if (slot[k] < 0) {
+                continue;                                   // a padding row: its keys and values are stored nowhere
+            } else if (c0 < Cq + Ck) {
+                const int c = c0 - Cq;
+                dst = kdst + (size_t)(c / d) * JANIS_PAGE * d + c % d;
+                if (wk != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < V; e += 4) Vec16<float>::load(wk + c + e, w + e);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) y[e] = y[e] * ik * w[e];
+                }
+            } else {
+                const int c = c0 - Cq - Ck, g = c / dv;
+                dst = vdst + (size_t)g * JANIS_PAGE * dv + c % dv;
+                const float iv = inv_s[k * (2 + G) + 2 + g];
+#pragma unroll
+                for (int e = 0; e < V; ++e) y[e] = y[e] * iv;
+            }
+            Vec16<T>::store(dst, y);
+        }
     }
 }
 
@@ -224,6 +409,42 @@ JANIS_EXPORT int janis_qkv_conv_norm_store(const void* rows, int dtype, int row_
     if (conv_w != nullptr && K > 1 && conv_state == nullptr) return fail("qkv_conv_norm_store: a filter needs its kept inputs");
     const size_t bytes = ((size_t)C + 2 + G + 32) * sizeof(float);
     if (bytes > 200 * 1024) return fail("qkv_conv_norm_store: a row of %lld channels does not fit shared memory", C);
+    // 16 bytes at a time where every head starts on such a border and the taps are few
+    const int taps = conv_w != nullptr ? K : 1;
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int V = dtype == JANIS_F32 ? 4 : 8;
+    const bool vec = taps <= 4 && d % V == 0 && dv % V == 0 && row_elems % V == 0 && aligned(rows) && aligned(q_out) &&
+                     aligned(kpool) && aligned(vpool) && aligned(conv_w) && aligned(conv_state) && aligned(wq) && aligned(wk);
+#define JANIS_PREP_VEC(TT, KT, TOK)                                                                                    \
+    {                                                                                                                  \
+        static size_t most = 0;                                                                                        \
+        const size_t vbytes = ((size_t)TOK * (C + 2 + G) + (PREP_THREADS / 32) * 2 * TOK) * sizeof(float);             \
+        if (vbytes > most && vbytes > 48 * 1024) {                                                                     \
+            cudaError_t e = cudaFuncSetAttribute(qkv_conv_norm_store_vec_kernel<TT, KT, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)vbytes); \
+            if (e != cudaSuccess) return fail("qkv_conv_norm_store: shared memory of %zu bytes refused: %s", vbytes, cudaGetErrorString(e)); \
+            most = vbytes;                                                                                             \
+        }                                                                                                              \
+        return launch_kernel("qkv_conv_norm_store", qkv_conv_norm_store_vec_kernel<TT, KT, TOK>,                       \
+                             dim3((T + TOK - 1) / TOK), dim3(PREP_THREADS), vbytes, stream, 1, (const TT*)rows,        \
+                             row_elems, T, H, G, d, dv, conv_w, conv_state, wq, wk, v_unit, eps, tok_pos, tok_seq,     \
+                             seq_slot, seq_first_row, seq_start, seq_end, (TT*)q_out, (TT*)kpool, (TT*)vpool,          \
+                             page_table, table_stride);                                                                \
+    }
+#define JANIS_PREP_VEC_TAPS(TT, TOK)                                                                                   \
+    {                                                                                                                  \
+        if (taps == 1) JANIS_PREP_VEC(TT, 1, TOK)                                                                      \
+        if (taps == 2) JANIS_PREP_VEC(TT, 2, TOK)                                                                      \
+        if (taps == 3) JANIS_PREP_VEC(TT, 3, TOK)                                                                      \
+        JANIS_PREP_VEC(TT, 4, TOK)                                                                                     \
+    }
+    // four rows a CTA where the step has rows enough to fill the GPU so and four filtered rows fit shared memory
+    const bool many = T >= PREP_MANY_ROWS && (size_t)4 * (C + 2 + G) * sizeof(float) <= 96 * 1024;
+    if (vec && many && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 4)
+    if (vec && many && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 4)
+    if (vec && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 1)
+    if (vec && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 1)
+#undef JANIS_PREP_VEC_TAPS
+#undef JANIS_PREP_VEC
 #define JANIS_PREP_LAUNCH(TT)                                                                                          \
     {                                                                                                                  \
         static size_t most = 0;                                                                                        \

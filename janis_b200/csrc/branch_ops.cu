@@ -57,7 +57,20 @@ rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* __restrict__ w, 
 // multiplied by w.  With a residual: v = alpha h[r] + res[r], h[r] = norm(v) (the stream itself is normed, in place)
 // and y[r] = h[r] rounded; without: y[r] = norm(h[src]) with src = rows[r] (or r), h untouched.
 // A group's sum runs over the lanes of its warps and then over its warps in index order.
-template <typename TR, typename TO>
+__device__ __forceinline__ void load4(const float* p, float* o) { Vec16<float>::load(p, o); }
+__device__ __forceinline__ void load4(const bf16* p, float* o) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+    o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float* v) { Vec16<float>::store(p, v); }
+__device__ __forceinline__ void store4(bf16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+// VEC: four elements a load and a store (a group's length is a multiple of four, and so is every row's start)
+template <typename TR, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 group_norm_kernel(float* __restrict__ h, const TR* __restrict__ res, const int* __restrict__ rows, float alpha,
                   const float* __restrict__ w, float eps, int groups, TO* __restrict__ y, int H) {
@@ -70,10 +83,23 @@ group_norm_kernel(float* __restrict__ h, const TR* __restrict__ res, const int* 
     grid_dependency_wait();
     const int src = rows != nullptr ? rows[r] : r;
     float* hr = h + (size_t)src * H;
-    for (int i = tid; i < H; i += blockDim.x) {
-        float v = hr[i];
-        if (res != nullptr) v = fmaf(alpha, v, to_float(res[(size_t)r * H + i]));
-        row_s[i] = v;
+    if (VEC) {
+        for (int i = tid * 4; i < H; i += blockDim.x * 4) {
+            float v[4], a[4];
+            load4(hr + i, v);
+            if (res != nullptr) {
+                load4(res + (size_t)r * H + i, a);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = fmaf(alpha, v[e], a[e]);
+            }
+            store4(row_s + i, v);
+        }
+    } else {
+        for (int i = tid; i < H; i += blockDim.x) {
+            float v = hr[i];
+            if (res != nullptr) v = fmaf(alpha, v, to_float(res[(size_t)r * H + i]));
+            row_s[i] = v;
+        }
     }
     const int gs = H / groups;
     const int wpg = nwarp / groups > 0 ? nwarp / groups : 1;      // warps that share a group
@@ -97,10 +123,23 @@ group_norm_kernel(float* __restrict__ h, const TR* __restrict__ res, const int* 
         }
     }
     __syncthreads();
-    for (int i = tid; i < H; i += blockDim.x) {
-        const float v = row_s[i] * inv_s[i / gs] * w[i];
-        if (res != nullptr) hr[i] = v;
-        if (y != nullptr) y[(size_t)r * H + i] = from_float<TO>(v);
+    if (VEC) {
+        for (int i = tid * 4; i < H; i += blockDim.x * 4) {
+            float v[4], ww[4];
+            load4(row_s + i, v);
+            load4(w + i, ww);
+            const float inv = inv_s[i / gs];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * ww[e];
+            if (res != nullptr) store4(hr + i, v);
+            if (y != nullptr) store4(y + (size_t)r * H + i, v);
+        }
+    } else {
+        for (int i = tid; i < H; i += blockDim.x) {
+            const float v = row_s[i] * inv_s[i / gs] * w[i];
+            if (res != nullptr) hr[i] = v;
+            if (y != nullptr) y[(size_t)r * H + i] = from_float<TO>(v);
+        }
     }
 }
 
@@ -353,16 +392,23 @@ JANIS_EXPORT int janis_group_norm(float* h, const void* res, int res_dtype, cons
     const size_t bytes = ((size_t)H + groups + 32) * sizeof(float);
     if (bytes > 200 * 1024) return fail("group_norm: a row of %d does not fit shared memory", H);
     const dim3 grid(R), block(H >= 1024 ? 256 : 128);
-#define JANIS_GN(TR, TO)                                                                                               \
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = (H / groups) % 4 == 0 && aligned(h) && aligned(res) && aligned(w) && aligned(y);
+#define JANIS_GN_V(TR, TO, VEC)                                                                                        \
     {                                                                                                                  \
         static size_t most = 0;                                                                                        \
         if (bytes > most && bytes > 48 * 1024) {                                                                       \
-            cudaError_t e = cudaFuncSetAttribute(group_norm_kernel<TR, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
+            cudaError_t e = cudaFuncSetAttribute(group_norm_kernel<TR, TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
             if (e != cudaSuccess) return fail("group_norm: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e)); \
             most = bytes;                                                                                              \
         }                                                                                                              \
-        return launch_kernel("group_norm", group_norm_kernel<TR, TO>, grid, block, bytes, stream, 1, h, (const TR*)res, rows, \
+        return launch_kernel("group_norm", group_norm_kernel<TR, TO, VEC>, grid, block, bytes, stream, 1, h, (const TR*)res, rows, \
                              alpha, w, eps, groups, (TO*)y, H);                                                        \
+    }
+#define JANIS_GN(TR, TO)                                                                                               \
+    {                                                                                                                  \
+        if (vec) JANIS_GN_V(TR, TO, true)                                                                              \
+        JANIS_GN_V(TR, TO, false)                                                                                      \
     }
     const int rd = res != nullptr ? res_dtype : JANIS_F32, yd = y != nullptr ? y_dtype : JANIS_F32;
     if (rd == JANIS_F32 && yd == JANIS_F32) JANIS_GN(float, float)
@@ -370,6 +416,7 @@ JANIS_EXPORT int janis_group_norm(float* h, const void* res, int res_dtype, cons
     if (rd == JANIS_BF16 && yd == JANIS_F32) JANIS_GN(bf16, float)
     if (rd == JANIS_BF16 && yd == JANIS_BF16) JANIS_GN(bf16, bf16)
 #undef JANIS_GN
+#undef JANIS_GN_V
     return fail("group_norm: unknown dtypes %d, %d", res_dtype, y_dtype);
 }
 

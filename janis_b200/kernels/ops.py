@@ -1153,10 +1153,13 @@ def latent_rotate_store(rows, lat_off: int, H: int, d: int, dr: int, R: int, wc,
     return qfull
 
 
+HEAD_LINEAR_FEW_ROWS = 64        # up to here the kernel that keeps its rows in shared memory; above, in bfloat16, the library's batched product
+
+
 def head_linear(x, x_head: int, x_off: int, w, out, o_head: int, o_off: int):
     """out[t, h * o_head + o_off + o] = sum_i w[h, o, i] x[t, h * x_head + x_off + i]: a product per head with a
     matrix of its own.  x [T, >= H x_head], w [H, O, I], out [T, >= H o_head], all of one dtype; float accumulation
-    in an order that depends on I alone."""
+    (in float32, and for few rows, in an order that depends on I alone)."""
     T = x.shape[0]
     Hn, O, I = w.shape
     _t(x, "x", _FLOATS, (T, None))
@@ -1164,6 +1167,13 @@ def head_linear(x, x_head: int, x_off: int, w, out, o_head: int, o_off: int):
     _t(out, "out", x.dtype, (T, None))
     if (Hn - 1) * x_head + x_off + I > x.shape[1] or (Hn - 1) * o_head + o_off + O > out.shape[1]:
         raise KernelError("head_linear: the heads do not fit the rows")
+    if x.dtype == torch.bfloat16 and T > HEAD_LINEAR_FEW_ROWS:
+        # many rows: the library's batched product (cuBLAS) over strided views, a batch entry per head, as
+        # `linear_bf16` takes the library product for its large cases
+        xv = x.as_strided((Hn, T, I), (x_head, x.stride(0), 1), x.storage_offset() + x_off)
+        ov = out.as_strided((Hn, T, O), (o_head, out.stride(0), 1), out.storage_offset() + o_off)
+        torch.bmm(xv, w.transpose(1, 2), out=ov)
+        return out
     lib = mixers()
     _check(lib, lib.janis_head_linear(x.data_ptr(), _DT[x.dtype], x.shape[1], int(x_head), int(x_off), w.data_ptr(),
                                       out.data_ptr(), out.shape[1], int(o_head), int(o_off), T, Hn, I, O, _stream()))

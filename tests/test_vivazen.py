@@ -394,19 +394,22 @@ def _tables(lens, starts, slots):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,K,norm,unit", [(4, 2, 32, 16, 4, True, True), (5, 5, 10, 6, 5, True, True), (2, 2, 16, 24, 0, True, True),
                                                   (6, 1, 16, 8, 2, False, False), (8, 2, 64, 64, 1, True, False), (3, 1, 8, 8, 16, True, True)])
-def test_filter_norm_store_kernel_against_its_statement(dtype, H, G, d, dv, K, norm, unit):
+@pytest.mark.parametrize("pad,lens", [(4, [7, 1, 70, 3, 2]), (16, [7, 1, 70, 3, 2]), (16, [601, 1, 515, 3, 2])])
+def test_filter_norm_store_kernel_against_its_statement(dtype, H, G, d, dv, K, norm, unit, pad, lens):
     """Sequences that start, that go on from inputs kept by an earlier step (across a page's border), that bring one
-    token, and a padding sequence; the filter's kept inputs, the queries and both pools are compared."""
+    token, and a padding sequence; the filter's kept inputs, the queries and both pools are compared.  (A step of
+    many rows runs the kernel whose CTAs take several rows.)"""
     from janis_b200.kernels import ops
     from tests import kernel_refs as R
     g = torch.Generator().manual_seed(5)
     C = H * d + G * (d + dv)
-    lens, starts, slots = [7, 1, 70, 3, 2], [0, 63, 60, 5, 0], [2, 0, 4, 1, -1]
+    starts, slots = [0, 63, 60, 5, 0], [2, 0, 4, 1, -1]
     tabs = _tables(lens, starts, slots)
     T = sum(lens)
-    n_pages = 16
-    table = torch.randperm(n_pages, generator=g)[:15].view(5, 3).to(torch.int32)
-    rows = torch.randn(T, C + 4, generator=g).to(dtype)
+    per_seq = max(-(-(a + n) // ops.PAGE) for a, n in zip(starts, lens))
+    n_pages = 5 * per_seq + 1
+    table = torch.randperm(n_pages, generator=g)[:5 * per_seq].view(5, per_seq).to(torch.int32)
+    rows = torch.randn(T, C + pad, generator=g).to(dtype)     # (rows of whole 16 bytes let the wide loads run)
     cw = torch.randn(C, K, generator=g).float() if K else None
     state = torch.randn(5, max(K - 1, 1), C, generator=g).float() if K > 1 else None
     wq, wk = (torch.randn(H * d, generator=g).float(), torch.randn(G * d, generator=g).float()) if norm else (None, None)
@@ -455,6 +458,12 @@ def test_latent_rows_and_head_products_against_their_statements(dtype, H, d, dr,
         R_.head_linear(rows, d + dr, 0, w, want_o, D, 0)
         ops.head_linear(rows.cuda(), d + dr, 0, w.cuda(), got_o, D, 0)
         _close(got_o, want_o, dtype, "products per head", f32=5e-5, bf16=3e-2)
+        few = ops.HEAD_LINEAR_FEW_ROWS // 8 + 1                  # few rows: the kernel of its own in every dtype
+        assert T > ops.HEAD_LINEAR_FEW_ROWS >= few
+        want_f, got_f = qfull[:few].clone(), qfull[:few].cuda()
+        R_.head_linear(rows[:few], d + dr, 0, w, want_f, D, 0)
+        ops.head_linear(rows[:few].cuda(), d + dr, 0, w.cuda(), got_f, D, 0)
+        _close(got_f, want_f, dtype, "products per head, few rows", f32=5e-5, bf16=3e-2)
 
 
 @GPU
