@@ -20,7 +20,7 @@
 namespace janis {
 
 constexpr int PREP_THREADS = 256;
-constexpr int PREP_MANY_ROWS = 1024;      // from here on a CTA of the wide kernel takes four rows
+constexpr int PREP_MANY_ROWS = 1024;      // from here on a CTA of the wide kernel takes four rows, or two
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
@@ -437,10 +437,14 @@ JANIS_EXPORT int janis_qkv_conv_norm_store(const void* rows, int dtype, int row_
         if (taps == 3) JANIS_PREP_VEC(TT, 3, TOK)                                                                      \
         JANIS_PREP_VEC(TT, 4, TOK)                                                                                     \
     }
-    // four rows a CTA where the step has rows enough to fill the GPU so and four filtered rows fit shared memory
-    const bool many = T >= PREP_MANY_ROWS && (size_t)4 * (C + 2 + G) * sizeof(float) <= 96 * 1024;
-    if (vec && many && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 4)
-    if (vec && many && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 4)
+    // four rows a CTA (or two) where the step has rows enough to fill the GPU so and as many filtered rows fit
+    // shared memory twice per SM
+    const size_t one_row = (size_t)(C + 2 + G) * sizeof(float);
+    const int per_cta = T < PREP_MANY_ROWS ? 1 : 4 * one_row <= 96 * 1024 ? 4 : 2 * one_row <= 96 * 1024 ? 2 : 1;
+    if (vec && per_cta == 4 && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 4)
+    if (vec && per_cta == 4 && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 4)
+    if (vec && per_cta == 2 && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 2)
+    if (vec && per_cta == 2 && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 2)
     if (vec && dtype == JANIS_F32) JANIS_PREP_VEC_TAPS(float, 1)
     if (vec && dtype == JANIS_BF16) JANIS_PREP_VEC_TAPS(bf16, 1)
 #undef JANIS_PREP_VEC_TAPS

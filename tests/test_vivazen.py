@@ -393,7 +393,8 @@ def _tables(lens, starts, slots):
 @GPU
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,K,norm,unit", [(4, 2, 32, 16, 4, True, True), (5, 5, 10, 6, 5, True, True), (2, 2, 16, 24, 0, True, True),
-                                                  (6, 1, 16, 8, 2, False, False), (8, 2, 64, 64, 1, True, False), (3, 1, 8, 8, 16, True, True)])
+                                                  (6, 1, 16, 8, 2, False, False), (8, 2, 64, 64, 1, True, False), (3, 1, 8, 8, 16, True, True),
+                                                  (32, 8, 128, 128, 3, True, True)])
 @pytest.mark.parametrize("pad,lens", [(4, [7, 1, 70, 3, 2]), (16, [7, 1, 70, 3, 2]), (16, [601, 1, 515, 3, 2])])
 def test_filter_norm_store_kernel_against_its_statement(dtype, H, G, d, dv, K, norm, unit, pad, lens):
     """Sequences that start, that go on from inputs kept by an earlier step (across a page's border), that bring one
