@@ -550,7 +550,7 @@ _TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_n
           "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act"),
           "nosolix": ("talk_attention", "qkv_rotate_store", "selective_scan", "causal_conv_silu", "gate_group_norm",
                       "moe_route", "moe_expert_act", "dyt_norm", "rmsnorm_accumulate", "sigmoid_gate", "bias_act"),
-          "vivazen": ("talk_attention", "qkv_conv_norm_store", "latent_rotate_store", "head_linear", "group_norm", "round_rows",
+          "vivazen": ("talk_attention", "talk_attention_rows", "qkv_conv_norm_store", "latent_rotate_store", "head_linear", "group_norm", "round_rows",
                       "sigmoid_gate", "gated_act")}
 
 
@@ -614,6 +614,8 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
                     state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
     att_name = "attn_prefill" if kind == "gemma2" else "talk_attention"
     dec_name = "attn_decode" if kind == "gemma2" else "talk_attention"
+    if kernels["decode_us"].get("talk_attention_rows"):      # decode steps through the kernels that take single rows
+        dec_name = "talk_attention_rows"
     scan_name = "selective_scan" if kind == "nosolix" else "gla_scan"
     roof = {}
     if kernels["prefill_us"].get(att_name):

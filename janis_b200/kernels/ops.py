@@ -141,6 +141,9 @@ def mixers():
         lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, F, P, I, I, P, c_longlong, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
+        lib.janis_talk_attention_rows_floats.argtypes = [I, I, I, I, I, I, I]
+        lib.janis_talk_attention_rows_floats.restype = c_longlong
+        lib.janis_talk_attention_rows.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, F, P, I, P, c_longlong, P]
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
         lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P, I, P]
@@ -854,6 +857,45 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         _stream()),
         kernels=(2 if two_pass else 1) *
                 (2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1))
+    return out
+
+
+def talk_attention_rows_floats(dtype, T: int, H: int, G: int, d: int, dv: int, max_keys: int) -> int:
+    """Floats of scratch that `talk_attention_rows` wants for a step of T rows that see up to max_keys keys each, or 0
+    where it does not take the sizes (heads that are no multiples of 16 bytes; scores of a chunk beyond shared memory)."""
+    return int(mixers().janis_talk_attention_rows_floats(_DT[dtype], int(T), int(H), int(G), int(d), int(dv), int(max_keys)))
+
+
+def talk_attention_rows(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, out, H: int, G: int, d: int,
+                        dv: int, scale: float, scratch, max_keys: int, sink: bool = False, window: int = 0, cap: float = 0.0,
+                        sink_values=None, values_in_keys: bool = False):
+    """`talk_attention` for a decode step (every row a query position of a sequence of its own): keys and values are
+    read once, 16 bytes a lane, a CTA per row and chunk of keys; scores are capped (cap > 0), seen inside the window
+    (window > 0), softmaxed with the sink (sink; sink_values [H] float32: learnt ones) and, with talk [H, H] float32,
+    the heads' weights mixed after the softmax; values_in_keys: the values are the first dv features of the keys.
+    q_rows [T, >= H d], out [T, H dv]; max_keys bounds the keys a row sees; scratch float32 of at least
+    `talk_attention_rows_floats`.  Sums are float and their order depends on the row alone."""
+    T = q_rows.shape[0]
+    _t(q_rows, "q_rows", _FLOATS, (T, None))
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", q_rows.dtype, (n_pages, G, PAGE, d))
+    if not values_in_keys:
+        _t(vpool, "vpool", q_rows.dtype, (n_pages, G, PAGE, dv))
+    if sink_values is not None and not sink:
+        raise KernelError("talk_attention_rows: sink values without a sink")
+    _t(page_table, "page_table", torch.int32, (None, None))
+    _t(out, "out", q_rows.dtype, (T, H * dv))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("talk_attention_rows: position tables shorter than the step")
+    lib = mixers()
+    _check(lib, lib.janis_talk_attention_rows(
+        q_rows.data_ptr(), _DT[q_rows.dtype], q_rows.shape[1], _t(tok_pos, "tok_pos", torch.int32),
+        _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32), kpool.data_ptr(),
+        None if values_in_keys else vpool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None, out.data_ptr(), T, H, G, d, dv,
+        float(scale), 1 if sink else 0, int(max_keys), int(window), float(cap),
+        _t(sink_values, "sink_values", torch.float32, (H,)) if sink_values is not None else None,
+        1 if values_in_keys else 0, _t(scratch, "scratch", torch.float32), scratch.numel(), _stream()), kernels=4)
     return out
 
 

@@ -101,6 +101,14 @@ class FilteredAttention(Mixer):
                                 ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, q, kv.k, kv.v, kv.table,
                                 one_token=decode)
         att = ws.buf("fattn.ctx", (T, H * dv), rt.dtype)
+        if decode and rt.dtype == torch.bfloat16:
+            # a decode step in the serving dtype: the kernels that take single rows and read keys and values once
+            n = ops.talk_attention_rows_floats(rt.dtype, T, H, G, d, dv, ctx.len_bound)
+            if n:
+                ops.talk_attention_rows(q, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, self.talk, att, H, G,
+                                        d, dv, self.scale, ws.buf("fattn.rows_scratch", (n,), torch.float32), ctx.len_bound,
+                                        cap=self.cap)
+                return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))
         stats = None
         if self.talk is not None:
             stats = ws.buf("fattn.stats", (ops.talk_attention_stats_floats(T, H),), torch.float32)

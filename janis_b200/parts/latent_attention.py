@@ -120,14 +120,24 @@ class LatentAttention(Mixer):
         mixed = ws.buf("lattn.mixed", (T, H * R), rt.dtype)                   # sum_j p c[j], head by head
         decode = ctx.mode == "decode"
         max_keys, n_chunks, scratch = 0, 1, None
-        if decode:
+        rows_floats = 0
+        if decode and rt.dtype == torch.bfloat16:
+            # a decode step in the serving dtype: the kernels that take single rows and read the cached rows once
+            max_keys = min(ctx.len_bound, self.window) if self.window else ctx.len_bound
+            rows_floats = ops.talk_attention_rows_floats(rt.dtype, T, H, 1, D, R, max_keys)
+        if rows_floats:
+            ops.talk_attention_rows(qfull, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, None, kv.table, None, mixed, H, 1, D, R,
+                                    self.scale, ws.buf("lattn.rows_scratch", (rows_floats,), torch.float32), max_keys,
+                                    sink=self.sink, window=self.window, sink_values=self.sink_values, values_in_keys=True)
+        elif decode:
             max_keys = min(ctx.len_bound, self.window) if self.window else ctx.len_bound
             n_chunks = max(1, min(rt.sm_count // max(T, 1), -(-max_keys // 128), 64))
             n = ops.talk_attention_scratch_floats(T, n_chunks, H, R)
             scratch = ws.buf("lattn.partial", (n,), torch.float32) if n else None
-        ops.talk_attention(qfull, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, None, kv.table, None, None, mixed, H, 1,
-                           D, R, self.scale, 0, self.sink, one_row=decode, max_keys=max_keys, n_chunks=n_chunks,
-                           scratch=scratch, window=self.window, sink_values=self.sink_values, values_in_keys=True)
+        if not rows_floats:
+            ops.talk_attention(qfull, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, None, kv.table, None, None, mixed, H, 1,
+                               D, R, self.scale, 0, self.sink, one_row=decode, max_keys=max_keys, n_chunks=n_chunks,
+                               scratch=scratch, window=self.window, sink_values=self.sink_values, values_in_keys=True)
         att = ws.buf("lattn.ctx", (T, H * dv), rt.dtype)
         ops.head_linear(mixed, R, 0, self.uv, att, dv, 0)
         if "g" in self.names:

@@ -378,6 +378,16 @@ def test_attention_kernel_options_against_their_statement(dtype, H, G, d, dv, wi
         finally:
             ops.talk_attention_set_kernel(1)
         _close(got, want, dtype, (which, one_row, chunks))
+    # the kernels that take single rows (decode steps), with bounds that cut a row's keys into one chunk and several
+    for bound in (min(w, 300), 5000):
+        n = ops.talk_attention_rows_floats(dtype, T, H, G, d, dv, bound)
+        assert (n > 0) == (d % (4 if dtype == torch.float32 else 8) == 0 and dv % (4 if dtype == torch.float32 else 8) == 0)
+        if n:
+            got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
+            ops.talk_attention_rows(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), None if in_keys else dev(vp),
+                                    dev(table), dev(M), got, H, G, d, dv, 0.4, torch.full((n,), float("nan"), device="cuda"),
+                                    bound, sink=sinks, window=window, cap=cap, sink_values=dev(sv), values_in_keys=in_keys)
+            _close(got, want, dtype, ("rows", bound))
 
 
 def _tables(lens, starts, slots):
