@@ -35,6 +35,23 @@ struct RowsShape {
     float scale, cap;
 };
 
+constexpr int ROWS_FLIGHT = 8;      // 16-byte loads a thread has in flight (kept as they came: four registers each)
+
+// 16 bytes as they came, and as floats
+template <typename T> __device__ __forceinline__ void rows_unpack(const uint4& raw, float* out);
+template <> __device__ __forceinline__ void rows_unpack<float>(const uint4& raw, float* out) {
+    out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+    out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void rows_unpack<bf16>(const uint4& raw, float* out) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {       // a bfloat16 is the upper half of a float
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
 __device__ __forceinline__ void rows_range(const RowsShape& sh, int pos, int c, int& j0, int& j1) {
     const int first = sh.window > 0 ? max(0, pos - sh.window + 1) : 0;
     j0 = first + c * sh.chunk;
@@ -76,7 +93,7 @@ rows_scores_kernel(const T* __restrict__ q_rows, int q_row_elems, const int* __r
         }
     }
     __syncthreads();
-    // `lanes` neighbouring lanes share a (key, key/value head) pair and take its 16-byte pieces in turn, four of them in
+    // `lanes` neighbouring lanes share a (key, key/value head) pair and take its 16-byte pieces in turn, eight of them in
     // flight a lane; their partial sums meet in a butterfly.  Every lane of a warp runs every pass (the last pairs repeat).
     const int P = sh.lanes, sub = tid % P, n_slots = ROWS_THREADS / P, n_pieces = d / V;
     for (int pair0 = 0; pair0 < n_pairs; pair0 += n_slots) {
@@ -87,21 +104,23 @@ rows_scores_kernel(const T* __restrict__ q_rows, int q_row_elems, const int* __r
             float acc[ROWS_HB];
 #pragma unroll
             for (int r = 0; r < ROWS_HB; ++r) acc[r] = 0.f;
-            for (int i0 = sub; i0 < n_pieces; i0 += 4 * P) {
-                float x[4][V];
+            for (int i0 = sub; i0 < n_pieces; i0 += ROWS_FLIGHT * P) {
+                uint4 raw[ROWS_FLIGHT];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (i0 + u * P < n_pieces) Vec16<T>::load(krow + (size_t)(i0 + u * P) * V, x[u]);
+                for (int u = 0; u < ROWS_FLIGHT; ++u) {
+                    if (i0 + u * P < n_pieces) raw[u] = *reinterpret_cast<const uint4*>(krow + (size_t)(i0 + u * P) * V);
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < ROWS_FLIGHT; ++u) {
                     if (i0 + u * P < n_pieces) {
+                        float x[V];
+                        rows_unpack<T>(raw[u], x);
 #pragma unroll
                         for (int r = 0; r < ROWS_HB; ++r) {
                             if (hb + r < rep) {
                                 const float* qh = q_s + (size_t)(g * rep + hb + r) * qs + (size_t)(i0 + u * P) * V;
 #pragma unroll
-                                for (int e = 0; e < V; ++e) acc[r] = fmaf(qh[e], x[u][e], acc[r]);
+                                for (int e = 0; e < V; ++e) acc[r] = fmaf(qh[e], x[e], acc[r]);
                             }
                         }
                     }
@@ -224,22 +243,25 @@ rows_values_kernel(const float* __restrict__ scores, const float* __restrict__ f
 #pragma unroll
                 for (int e = 0; e < V; ++e) acc[r][e] = 0.f;
             if (live) {
-                for (int jj = sub; jj < n_keys; jj += 4 * share) {          // four keys in flight, added in ascending order
-                    float x[4][V];
+                for (int jj = sub; jj < n_keys; jj += ROWS_FLIGHT * share) {      // keys in flight, added in ascending order
+                    uint4 raw[ROWS_FLIGHT];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    for (int k = 0; k < ROWS_FLIGHT; ++k) {
                         if (jj + k * share < n_keys)
-                            Vec16<T>::load(vpool + ((size_t)base_s[jj + k * share] + (size_t)g * JANIS_PAGE) * sh.v_stride + c0, x[k]);
+                            raw[k] = *reinterpret_cast<const uint4*>(
+                                vpool + ((size_t)base_s[jj + k * share] + (size_t)g * JANIS_PAGE) * sh.v_stride + c0);
                     }
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    for (int k = 0; k < ROWS_FLIGHT; ++k) {
                         if (jj + k * share < n_keys) {
+                            float x[V];
+                            rows_unpack<T>(raw[k], x);
 #pragma unroll
                             for (int r = 0; r < VB; ++r) {
                                 if (hb + r < rep) {
                                     const float p = p_s[(size_t)(g * rep + hb + r) * chunk + jj + k * share];
 #pragma unroll
-                                    for (int e = 0; e < V; ++e) acc[r][e] = fmaf(p, x[k][e], acc[r][e]);
+                                    for (int e = 0; e < V; ++e) acc[r][e] = fmaf(p, x[e], acc[r][e]);
                                 }
                             }
                         }
