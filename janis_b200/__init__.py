@@ -15,11 +15,13 @@ from .config.gemma2 import Gemma2Config
 from .config.sigalorn import SigalornConfig
 from .config.nosolix import NosolixConfig
 from .config.vivazen import VivazenConfig
+from .config.dekutar import DekutarConfig
 from .registry import architectures, register_architecture, resolve, unregister_architecture
 from .models import gemma2 as _gemma2            # registers Gemma2ForCausalLM
 from .models import sigalorn as _sigalorn        # registers Sigalorn
 from .models import nosolix as _nosolix          # registers Nosolix
 from .models import vivazen as _vivazen          # registers Vivazen
+from .models import dekutar as _dekutar          # registers Dekutar
 from .engine.engine import Engine, build_model, from_config, load, open, write_random_model
 from .engine.step import StepEntry, StepError
 from .engine.generate import Reply
@@ -29,5 +31,5 @@ from .weights.loader import WeightsError
 __version__ = "0.1.0"
 
 __all__ = ["open", "load", "from_config", "write_random_model", "build_model", "Engine", "StepEntry", "StepError",
-           "Reply", "SamplingParams", "Gemma2Config", "SigalornConfig", "NosolixConfig", "VivazenConfig", "ConfigError", "WeightsError", "register_architecture",
+           "Reply", "SamplingParams", "Gemma2Config", "SigalornConfig", "NosolixConfig", "VivazenConfig", "DekutarConfig", "ConfigError", "WeightsError", "register_architecture",
            "unregister_architecture", "architectures", "resolve", "__version__"]

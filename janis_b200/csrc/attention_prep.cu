@@ -299,11 +299,14 @@ qkv_conv_norm_store_vec_kernel(const T* __restrict__ rows, int row_elems, int n_
     }
 }
 
-// rows[t]: q (H heads of d + dr) at 0, then at lat_off the compressed row [c (R) | r (dr)].
+// rows[t]: q (H heads of d + dr) at 0 (or the rows of q_rows, when the queries come from a product of their own), and
+// at lat_off the compressed row [c (R) | r (dr)].
 // qfull[t, h, R : R + dr] = turn(q[t, h, d : d + dr]); the line's key at the token's position = [norm(c) | turn(r)].
+// The turned pairs are neighbours (2p, 2p + 1) or, with `halves`, (p, p + rot/2); features from `rot` on pass as they are.
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_rotate_store_kernel(const T* __restrict__ rows, int row_elems, int lat_off, int H, int d, int dr, int rot, int R,
+latent_rotate_store_kernel(const T* __restrict__ rows, int row_elems, int lat_off, const T* __restrict__ q_rows,
+                           int q_row_elems, int halves, int H, int d, int dr, int rot, int R,
                            const float* __restrict__ wc, float eps, const float* __restrict__ inv_freq, float amp,
                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                            const int* __restrict__ seq_slot, T* __restrict__ qfull, T* __restrict__ kpool,
@@ -319,6 +322,7 @@ latent_rotate_store_kernel(const T* __restrict__ rows, int row_elems, int lat_of
     }
     grid_dependency_wait();
     const T* row = rows + (size_t)t * row_elems;
+    const T* qrow = q_rows != nullptr ? q_rows + (size_t)t * q_row_elems : row;
     const T* lat = row + lat_off;
     float ss = 0.f;
     for (int c = tid; c < R; c += nt) {
@@ -339,19 +343,85 @@ latent_rotate_store_kernel(const T* __restrict__ rows, int row_elems, int lat_of
             sn *= amp;
             cs *= amp;
         }
-        const T* src = unit == 0 ? lat + R : row + (size_t)(unit - 1) * (d + dr) + d;
-        const float a = to_float(src[2 * p]), b = to_float(src[2 * p + 1]);
+        const T* src = unit == 0 ? lat + R : qrow + (size_t)(unit - 1) * (d + dr) + d;
+        // where the pair sits: neighbours, or half the turned width apart (the pairs that pass lie behind the turned ones)
+        const int ia = !halves ? 2 * p : (2 * p < rot ? p : 2 * p), ib = !halves ? 2 * p + 1 : (2 * p < rot ? p + (rot >> 1) : 2 * p + 1);
+        const float a = to_float(src[ia]), b = to_float(src[ib]);
         const float lo = a * cs - b * sn, hi = b * cs + a * sn;
         if (unit == 0) {
             if (kdst != nullptr) {
-                kdst[R + 2 * p] = from_float<T>(lo);
-                kdst[R + 2 * p + 1] = from_float<T>(hi);
+                kdst[R + ia] = from_float<T>(lo);
+                kdst[R + ib] = from_float<T>(hi);
             }
         } else {
             T* dst = qfull + ((size_t)t * H + (unit - 1)) * D + R;
-            dst[2 * p] = from_float<T>(lo);
-            dst[2 * p + 1] = from_float<T>(hi);
+            dst[ia] = from_float<T>(lo);
+            dst[ib] = from_float<T>(hi);
         }
+    }
+}
+
+// Queries and keys that are turned and then divided by their own root mean square, head by head, and values that are
+// the keys as they were projected.  rows[t]: q (H heads of d) at 0, k (G heads of d) behind them.  The first `rot`
+// features of every head turn by the token's position (pairs (2p, 2p + 1), or (p, p + rot/2) with `halves`; angle
+// pos * inv_freq[p]); with unit_norm every head is then divided by sqrt(mean(head^2) + eps).  q is written back in
+// place; k goes to the line's keys at the token's position and, when vpool is given, k as projected to its values.
+// A CTA per token, a warp per head; the head passes through shared memory as floats.
+constexpr int QKN_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(QKN_WARPS * 32)
+qk_rotate_norm_store_kernel(T* __restrict__ rows, int row_elems, int H, int G, int d, int rot, int halves,
+                            const float* __restrict__ inv_freq, int unit_norm, float eps,
+                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                            const int* __restrict__ seq_slot, T* __restrict__ kpool, T* __restrict__ vpool,
+                            const int* __restrict__ page_table, int table_stride) {
+    extern __shared__ float qkn_smem[];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = qkn_smem + (size_t)warp * d;
+    grid_dependents_launch();
+    const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
+    size_t kat = 0;
+    if (slot >= 0) {
+        const int page = page_table[(size_t)slot * table_stride + pos / JANIS_PAGE];
+        kat = ((size_t)page * G * JANIS_PAGE + pos % JANIS_PAGE) * d;
+    }
+    grid_dependency_wait();
+    T* row = rows + (size_t)t * row_elems;
+    const int hr = rot >> 1;
+    for (int head = warp; head < H + G; head += QKN_WARPS) {
+        const bool is_key = head >= H;
+        if (is_key && slot < 0) continue;                    // a padding row's keys are stored nowhere
+        T* src = row + (size_t)head * d;
+        T* kd = is_key ? kpool + kat + (size_t)(head - H) * JANIS_PAGE * d : nullptr;
+        T* vd = is_key && vpool != nullptr ? vpool + kat + (size_t)(head - H) * JANIS_PAGE * d : nullptr;
+        float ss = 0.f;
+        for (int p = lane; p < hr; p += 32) {
+            const int ia = halves ? p : 2 * p, ib = halves ? p + hr : 2 * p + 1;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[p], &sn, &cs);
+            const T ra = src[ia], rb = src[ib];
+            const float a = to_float(ra), b = to_float(rb);
+            const float lo = a * cs - b * sn, hi = b * cs + a * sn;
+            buf[ia] = lo;
+            buf[ib] = hi;
+            ss = fmaf(lo, lo, ss);
+            ss = fmaf(hi, hi, ss);
+            if (vd != nullptr) { vd[ia] = ra; vd[ib] = rb; }
+        }
+        for (int c = rot + lane; c < d; c += 32) {
+            const T r = src[c];
+            const float v = to_float(r);
+            buf[c] = v;
+            ss = fmaf(v, v, ss);
+            if (vd != nullptr) vd[c] = r;
+        }
+        ss = warp_sum(ss);
+        const float inv = unit_norm ? 1.f / sqrtf(ss / (float)d + eps) : 1.f;
+        __syncwarp();
+        T* dst = is_key ? kd : src;
+        for (int c = lane; c < d; c += 32) dst[c] = from_float<T>(buf[c] * inv);
+        __syncwarp();
     }
 }
 
@@ -468,23 +538,46 @@ JANIS_EXPORT int janis_qkv_conv_norm_store(const void* rows, int dtype, int row_
     return fail("qkv_conv_norm_store: unknown dtype %d", dtype);
 }
 
-JANIS_EXPORT int janis_latent_rotate_store(const void* rows, int dtype, int row_elems, int lat_off, int T, int H, int d,
+JANIS_EXPORT int janis_latent_rotate_store(const void* rows, int dtype, int row_elems, int lat_off, const void* q_rows,
+                                           int q_row_elems, int halves, int T, int H, int d,
                                            int dr, int rot, int R, const float* wc, float eps, const float* inv_freq, float amp,
                                            const int* tok_pos, const int* tok_seq, const int* seq_slot, void* qfull,
                                            void* kpool, const int* page_table, int table_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || d < 0 || dr < 0 || (dr & 1) || R <= 0) return fail("latent_rotate_store: sizes %d heads, %d + %d, rank %d", H, d, dr, R);
     if (rot < 0 || (rot & 1) || rot > dr) return fail("latent_rotate_store: %d of %d features turned", rot, dr);
-    if (lat_off < H * (d + dr) || lat_off + R + dr > row_elems) return fail("latent_rotate_store: rows of %d elements are too short", row_elems);
+    if (lat_off < (q_rows == nullptr ? H * (d + dr) : 0) || lat_off + R + dr > row_elems || (q_rows != nullptr && q_row_elems < H * (d + dr)))
+        return fail("latent_rotate_store: rows of %d elements are too short", row_elems);
     if (dtype == JANIS_F32)
         return launch_kernel("latent_rotate_store", latent_rotate_store_kernel<float>, dim3(T), dim3(128), 0, stream, 1,
-                             (const float*)rows, row_elems, lat_off, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
+                             (const float*)rows, row_elems, lat_off, (const float*)q_rows, q_row_elems, halves, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
                              seq_slot, (float*)qfull, (float*)kpool, page_table, table_stride);
     if (dtype == JANIS_BF16)
         return launch_kernel("latent_rotate_store", latent_rotate_store_kernel<bf16>, dim3(T), dim3(128), 0, stream, 1,
-                             (const bf16*)rows, row_elems, lat_off, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
+                             (const bf16*)rows, row_elems, lat_off, (const bf16*)q_rows, q_row_elems, halves, H, d, dr, rot, R, wc, eps, inv_freq, amp, tok_pos, tok_seq,
                              seq_slot, (bf16*)qfull, (bf16*)kpool, page_table, table_stride);
     return fail("latent_rotate_store: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_qk_rotate_norm_store(void* rows, int dtype, int row_elems, int T, int H, int G, int d, int rot,
+                                            int halves, const float* inv_freq, int unit_norm, float eps,
+                                            const int* tok_pos, const int* tok_seq, const int* seq_slot, void* kpool,
+                                            void* vpool, const int* page_table, int table_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || d <= 0) return fail("qk_rotate_norm_store: sizes %d heads over %d, %d", H, G, d);
+    if (rot < 0 || (rot & 1) || rot > d) return fail("qk_rotate_norm_store: %d of %d features turned", rot, d);
+    if ((H + G) * d > row_elems) return fail("qk_rotate_norm_store: rows of %d elements are too short", row_elems);
+    const size_t smem = (size_t)QKN_WARPS * d * sizeof(float);
+    if (smem > 48 * 1024) return fail("qk_rotate_norm_store: heads of %d features do not fit shared memory", d);
+    if (dtype == JANIS_F32)
+        return launch_kernel("qk_rotate_norm_store", qk_rotate_norm_store_kernel<float>, dim3(T), dim3(QKN_WARPS * 32), smem,
+                             stream, 1, (float*)rows, row_elems, H, G, d, rot, halves, inv_freq, unit_norm, eps, tok_pos,
+                             tok_seq, seq_slot, (float*)kpool, (float*)vpool, page_table, table_stride);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("qk_rotate_norm_store", qk_rotate_norm_store_kernel<bf16>, dim3(T), dim3(QKN_WARPS * 32), smem,
+                             stream, 1, (bf16*)rows, row_elems, H, G, d, rot, halves, inv_freq, unit_norm, eps, tok_pos,
+                             tok_seq, seq_slot, (bf16*)kpool, (bf16*)vpool, page_table, table_stride);
+    return fail("qk_rotate_norm_store: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT int janis_head_linear(const void* x, int dtype, int x_stride, int x_head, int x_off, const void* w, void* out,

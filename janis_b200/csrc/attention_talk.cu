@@ -6,7 +6,8 @@
 //   o_h[i]        = sum_j p_h[i, j] v_kv(h)[j]
 //
 // A key j is seen by the query at position i when j <= i and, with a block size B > 0, floor(j / B) ==
-// floor(i / B), and, with a window W > 0, i - j < W.  sink is 1 (a key of score 0 without a value) or 0.  Keys have `d` features and values `dv`,
+// floor(i / B), and, with a window W > 0, i - j < W or j < keep_first (the sequence's first positions stay seen behind the
+// window, at their true positions).  sink is 1 (a key of score 0 without a value) or 0.  Keys have `d` features and values `dv`,
 // which need not be equal.  Values may be stored rotated by their own position (pairs m, m + dv/2, angle
 // j * inv_v[m]); the head's output is then turned back by the query's position.
 //
@@ -113,6 +114,7 @@ struct TalkShape {
     int block;          // keys are seen within blocks of this many positions (0: all earlier keys)
     int sink;           // 1: one is added to the softmax's denominator
     int window;         // keys are seen among the query's last `window` positions (0: no such limit)
+    int keep_first;     // with a window: the sequence's first `keep_first` positions stay seen behind it
     int kt;             // keys per tile (<= 32)
     float scale;
     float cap;          // > 0: raw <- cap tanh(raw / cap)
@@ -180,18 +182,20 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
     }
     int first = sh.block > 0 ? (pos / sh.block) * sh.block : 0;
     if (sh.window > 0) first = max(first, pos - sh.window + 1);
+    // the keys a row sees, counted through: the kept first positions that lie before the window, then first .. pos
+    const int kept = sh.window > 0 ? min(sh.keep_first, first) : 0, n_keys = kept + pos - first + 1;
     const int* table = page_table + (size_t)slot * table_stride;
-    for (int j0 = first; j0 <= pos; j0 += KT) {
-        const int kt = min(KT, pos - j0 + 1);
+    for (int j0 = 0; j0 < n_keys; j0 += KT) {
+        const int kt = min(KT, n_keys - j0);
         __syncthreads();                              // the tile before has been used; q_s and o_s are in place
         for (int u = tid; u < kt * G * d; u += nt) {
-            const int jj = u / (G * d), r = u % (G * d), g = r / d, c = r % d, j = j0 + jj;
+            const int jj = u / (G * d), r = u % (G * d), g = r / d, c = r % d, j = j0 + jj < kept ? j0 + jj : first + j0 + jj - kept;
             const size_t at = (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * d + c;
             k_s[(size_t)jj * kstride + r] = to_float(kpool[at]);
         }
         if (sh.mode != 1)
             for (int u = tid; u < kt * G * dv; u += nt) {
-                const int jj = u / (G * dv), r = u % (G * dv), g = r / dv, c = r % dv, j = j0 + jj;
+                const int jj = u / (G * dv), r = u % (G * dv), g = r / dv, c = r % dv, j = j0 + jj < kept ? j0 + jj : first + j0 + jj - kept;
                 const size_t at = (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * sh.v_stride + c;
                 v_s[(size_t)jj * G * dv + r] = to_float(vpool[at]);
             }
@@ -324,6 +328,7 @@ constexpr int TALK_MMA_WARPS = 16, TALK_MMA_THREADS = TALK_MMA_WARPS * 32;
 struct TalkMmaShape {
     int H, G, d, dv, block, sink;
     int window;         // keys are seen among the query's last `window` positions (0: no such limit)
+    int keep_first;     // with a window: the sequence's first `keep_first` positions stay seen behind it
     int qr;             // rows of the operands kept (16 or 8; 1 in a decode step, whose CTAs own one row each)
     int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
     int bn;             // keys per tile (16, 32, 64)
@@ -356,7 +361,7 @@ __host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, in
     L.corr = at; at += (size_t)hp * qr * 4;
     L.talk = at; at += (size_t)H * H * 4;
     L.fin = at;  at += (size_t)2 * H * qr * 4;          // mode 2: every (head, row)'s final maximum and 1 / denominator
-    L.meta = at; at += (3 * 16 + 64) * 4;
+    L.meta = at; at += (3 * 16 + 2 * 64) * 4;
     L.total = at;
     return L;
 }
@@ -388,6 +393,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     int* seq_s = pos_s + 16;
     int* slot_s = pos_s + 32;
     int* base_s = pos_s + 48;                  // where each key of the tile starts in the pools (in rows), -1 beyond the last
+    int* kpos_s = pos_s + 112;                 // each key's position in its sequence
     const bool split = sh.chunk > 0;           // the CTA leaves a partial result; the sink joins at the merge
     const int bn_log2 = BN == 64 ? 6 : (BN == 32 ? 5 : 4);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -440,16 +446,21 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         if (slot >= 0) {
             int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
             if (sh.window > 0) first = max(first, pos_s[a] - sh.window + 1);       // the run's first row reaches back farthest
+            // the keys the run sees, counted through: the kept first positions that lie before the window, then
+            // first .. last; a decode row's chunks cut this count
+            const int kept = sh.window > 0 ? min(sh.keep_first, first) : 0;
+            int n_first = 0, n_last = kept + last - first;
             if (split) {
-                first += ((int)blockIdx.y / sh.hg) * sh.chunk;
-                last = min(last, first + sh.chunk - 1);
+                n_first = ((int)blockIdx.y / sh.hg) * sh.chunk;
+                n_last = min(n_last, n_first + sh.chunk - 1);
             }
             const int* table = page_table + (size_t)slot * table_stride;
-            for (int j0 = first; j0 <= last; j0 += BN) {
+            for (int j0 = n_first; j0 <= n_last; j0 += BN) {
                 // ---- keys of the tile
                 if (tid < BN) {
-                    const int j = j0 + tid;
-                    base_s[tid] = j <= last ? (table[j / JANIS_PAGE] * G) * JANIS_PAGE + j % JANIS_PAGE : -1;
+                    const int n = j0 + tid, j = n < kept ? n : first + n - kept;
+                    base_s[tid] = n <= n_last ? (table[j / JANIS_PAGE] * G) * JANIS_PAGE + j % JANIS_PAGE : -1;
+                    kpos_s[tid] = j;
                 }
                 __syncthreads();
                 // (a warp per row of the tile, a lane per 16 bytes: no divisions in the addresses)
@@ -516,10 +527,10 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 __syncthreads();
                 // ---- 2a: the heads' scores mixed, the mask
                 for (int pair = tid; pair < QR * BN; pair += TALK_MMA_THREADS) {
-                    const int r = pair >> bn_log2, c = pair & (BN - 1), j = j0 + c;
-                    bool seen = r >= a && r < b && j <= pos_s[r];
+                    const int r = pair >> bn_log2, c = pair & (BN - 1), j = kpos_s[c];
+                    bool seen = r >= a && r < b && j <= pos_s[r] && base_s[c] >= 0;
                     if (seen && sh.block > 0) seen = j >= (pos_s[r] / sh.block) * sh.block;
-                    if (seen && sh.window > 0) seen = j > pos_s[r] - sh.window;
+                    if (seen && sh.window > 0) seen = j > pos_s[r] - sh.window || j < sh.keep_first;
                     float* at = raw_s + (size_t)r * L.rs + c;
                     const size_t hs = (size_t)QR * L.rs;
                     if (sh.mode == 2) {
@@ -893,7 +904,7 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
                                       void* out, int T, int H, int G, int d, int dv, float scale, int block, int sink,
                                       int one_row, int max_keys, int n_chunks, float* partial, long long partial_floats,
                                       int window, float cap, const float* sink_vals, int mix_after, int v_in_keys,
-                                      float* stats, long long stats_floats, cudaStream_t stream) {
+                                      float* stats, long long stats_floats, int keep_first, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) return fail("talk_attention: %d query heads do not divide over %d key/value heads", H, G);
     if (d <= 0 || dv <= 0) return fail("talk_attention: key size %d, value size %d", d, dv);
@@ -901,6 +912,8 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     if (q_row_elems < H * d) return fail("talk_attention: query rows of %d elements are too short", q_row_elems);
     if (block < 0) return fail("talk_attention: block size %d", block);
     if (window < 0) return fail("talk_attention: window %d", window);
+    if (keep_first < 0 || (keep_first > 0 && (window <= 0 || block > 0)))
+        return fail("talk_attention: %d kept first positions need a window and no blocks", keep_first);
     if (v_in_keys && (dv > d || inv_v != nullptr)) return fail("talk_attention: values of %d features do not lie in keys of %d", dv, d);
     if (sink_vals != nullptr && !sink) return fail("talk_attention: sink values without a sink");
     const bool two_pass = mix_after && talk != nullptr;       // (without a matrix there is nothing to mix: one pass)
@@ -912,7 +925,7 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
         size_t mma_bytes = 0;
         TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
         if (ms.qr) {
-            ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale; ms.window = window;
+            ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale; ms.window = window; ms.keep_first = keep_first;
             ms.cap = cap; ms.mode = 0; ms.v_in_keys = v_in_keys ? 1 : 0;
             if (one_row && n_chunks > 1 && max_keys > 0 && partial != nullptr) {
                 // a decode row's keys over n_chunks CTAs, each a whole number of tiles
@@ -933,7 +946,7 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     }
     size_t bytes = 0;
     TalkShape sh;
-    sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale; sh.window = window;
+    sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale; sh.window = window; sh.keep_first = keep_first;
     sh.cap = cap; sh.mode = 0; sh.v_stride = v_in_keys ? d : dv;
     sh.kt = talk_plain_tile(H, G, d, dv, &bytes);
     if (sh.kt == 0) return fail("talk_attention: heads of these sizes do not fit shared memory (%d x %d, %d x %d)", H, d, G, dv);

@@ -172,7 +172,9 @@ sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ rows, int row_elems
 // groups of neighbours, a group's score is the sum of its two largest c, the best `keep` groups stay (ties: the
 // lower index); among their experts the `top` of largest c are chosen (ties: the lower index); the chosen get
 // w_e = s_e / (sum of the chosen s + 1e-20) * scale, every other expert 0.  With a shared gate, column E of z is
-// its logit and column E of the output its sigmoid.
+// its logit and column E of the output its sigmoid.  With `softmax` the scores are the softmax of z over all entries instead.  With
+// n_identity > 0 the router scores that many entries more, behind the experts (no groups then); they have no column of
+// their own in the output: the weights of the chosen ones add up in its last column.
 // ---------------------------------------------------------------------------
 constexpr int ROUTE_WARPS = 4;
 
@@ -187,25 +189,38 @@ __device__ __forceinline__ void warp_argmax(float& v, int& at) {
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E, int n_groups, int keep,
-                 int top, float scale, int shared_gate, float* __restrict__ out) {
+                 int top, float scale, int shared_gate, float* __restrict__ out, int n_identity, int softmax) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * ROUTE_WARPS + warp;
-    float* s = smem + (size_t)warp * (3 * E);        // scores
-    float* c = s + E;                                // choice scores (minus infinity once out of the running)
-    float* gs = c + E;                               // group scores
+    const int N = E + n_identity;                    // entries the router scores: the experts, then the identity entries
+    float* s = smem + (size_t)warp * (4 * N);        // scores
+    float* c = s + N;                                // choice scores (minus infinity once out of the running)
+    float* gs = c + N;                               // group scores
+    float* mark = gs + N;                            // 1 for the chosen
     grid_dependents_launch();
     grid_dependency_wait();
     if (t >= T) return;
-    const int cols = E + (shared_gate ? 1 : 0), per = E / n_groups;
-    const float* zr = z + (size_t)t * cols;
-    float* o = out + (size_t)t * cols;
-    for (int e = lane; e < E; e += 32) {
-        const float v = 1.0f / (1.0f + expf(-zr[e]));
+    const int cols_in = N + (shared_gate ? 1 : 0), cols_out = E + (shared_gate ? 1 : 0) + (n_identity ? 1 : 0), per = N / n_groups;
+    const float* zr = z + (size_t)t * cols_in;
+    float* o = out + (size_t)t * cols_out;
+    float zmax = -CUDART_INF_F, zsum = 0.f;
+    if (softmax) {
+        for (int e = lane; e < N; e += 32) zmax = fmaxf(zmax, zr[e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < N; e += 32) {
+            const float v = expf(zr[e] - zmax);
+            s[e] = v;
+            zsum += v;
+        }
+        zsum = warp_sum(zsum);
+    }
+    for (int e = lane; e < N; e += 32) {
+        const float v = softmax ? s[e] / zsum : 1.0f / (1.0f + expf(-zr[e]));
         s[e] = v;
         c[e] = v + correction[e];
-        o[e] = 0.f;
+        mark[e] = 0.f;
     }
-    if (shared_gate && lane == 0) o[E] = 1.0f / (1.0f + expf(-zr[E]));
+    if (shared_gate && lane == 0) o[E] = 1.0f / (1.0f + expf(-zr[N]));
     __syncwarp();
     if (n_groups > 1 && keep < n_groups) {
         for (int g = lane; g < n_groups; g += 32) {
@@ -231,7 +246,7 @@ moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correcti
             if (lane == 0 && at < n_groups) gs[at] = CUDART_INF_F;
             __syncwarp();
         }
-        for (int e = lane; e < E; e += 32)
+        for (int e = lane; e < N; e += 32)
             if (gs[e / per] != CUDART_INF_F) c[e] = -CUDART_INF_F;
         __syncwarp();
     }
@@ -239,33 +254,52 @@ moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correcti
     for (int k = 0; k < top; ++k) {
         float v = -CUDART_INF_F;
         int at = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
+        for (int e = lane; e < N; e += 32) {
             const float cv = c[e];
             if (cv > v || (cv == v && e < at)) { v = cv; at = e; }
         }
         warp_argmax(v, at);
         __syncwarp();
-        if (at >= E) break;                          // nothing left in the running
+        if (at >= N) break;                          // nothing left in the running
         total += s[at];
         if (lane == 0) {
             c[at] = -CUDART_INF_F;
-            o[at] = -1.f;                            // marked; weighed below
+            mark[at] = 1.f;
         }
         __syncwarp();
     }
     const float f = scale / (total + 1e-20f);
-    for (int e = lane; e < E; e += 32)
-        if (o[e] < 0.f) o[e] = s[e] * f;
+    for (int e = lane; e < E; e += 32) o[e] = mark[e] != 0.f ? s[e] * f : 0.f;
+    if (n_identity) {
+        float id = 0.f;                              // the identity entries' weights add up: they all return the input
+        for (int e = E + lane; e < N; e += 32)
+            if (mark[e] != 0.f) id += s[e] * f;
+        id = warp_sum(id);
+        if (lane == 0) o[cols_out - 1] = id;
+    }
 }
 
-// a[t, col] = w[t, e] * g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), over the
+// out[t, :] += w[t] y[t, :], w[t] = wts[t, w_col]: what the chosen identity entries of a mixture add to its output
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_identity_add_kernel(T* __restrict__ out, const T* __restrict__ y, const float* __restrict__ wts, int wts_stride, int w_col,
+                        int width, size_t n) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float w = wts[(i / width) * wts_stride + w_col];
+        if (w != 0.f) out[i] = from_float<T>(fmaf(w, to_float(y[i]), to_float(out[i])));
+    }
+}
+
+// a[t, col] = w[t, e] * g sigmoid(alpha g) (u + up_add), g = min(gate, limit), u = clamp(up, -limit, limit), over the
 // columns of all experts side by side (expert e: `ff` columns; then the shared expert's `shared_ff`); in gu an
 // expert's gate columns are followed by its up columns.  Experts of weight 0 give exact zeros.
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_expert_act_kernel(const T* __restrict__ gu, const float* __restrict__ wts, int E, int ff, float limit, int shared_ff,
-                      float shared_limit, float alpha, T* __restrict__ out, size_t n) {
-    const int total = E * ff + shared_ff, wcols = E + (shared_ff ? 1 : 0);
+                      float shared_limit, float alpha, T* __restrict__ out, size_t n, int wcols, float up_add) {
+    const int total = E * ff + shared_ff;
     grid_dependents_launch();
     grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -282,7 +316,7 @@ moe_expert_act_kernel(const T* __restrict__ gu, const float* __restrict__ wts, i
             const T* row = gu + t * (size_t)(2 * total) + base;
             const float g = fminf(to_float(row[j]), lim);
             const float u = fminf(fmaxf(to_float(row[width + j]), -lim), lim);
-            a = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+            a = w * (g / (1.0f + expf(-alpha * g))) * (u + up_add);
         }
         out[i] = from_float<T>(a);
     }
@@ -293,9 +327,9 @@ moe_expert_act_kernel(const T* __restrict__ gu, const float* __restrict__ wts, i
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_expert_act_vec_kernel(const T* __restrict__ gu, const float* __restrict__ wts, int E, int ff, float limit, int shared_ff,
-                          float shared_limit, float alpha, T* __restrict__ out, int T_rows) {
+                          float shared_limit, float alpha, T* __restrict__ out, int T_rows, int wcols, float up_add) {
     constexpr int V = Vec16<T>::N;
-    const int total = E * ff + shared_ff, wcols = E + (shared_ff ? 1 : 0), per_row = total / V;
+    const int total = E * ff + shared_ff, per_row = total / V;
     grid_dependents_launch();
     grid_dependency_wait();
     for (int t = blockIdx.y; t < T_rows; t += gridDim.y) {
@@ -321,7 +355,7 @@ moe_expert_act_vec_kernel(const T* __restrict__ gu, const float* __restrict__ wt
                 for (int i = 0; i < V; ++i) {
                     const float g = fminf(gv[i], lim);
                     const float u = fminf(fmaxf(uv[i], -lim), lim);
-                    a[i] = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                    a[i] = w * (g / (1.0f + expf(-alpha * g))) * (u + up_add);
                 }
             }
             Vec16<T>::store(orow + col, a);
@@ -426,19 +460,37 @@ JANIS_EXPORT int janis_round_rows(const float* h, void* y, size_t n, cudaStream_
 }
 
 JANIS_EXPORT int janis_moe_route(const float* z, const float* correction, int T, int E, int n_groups, int keep, int top,
-                                 float scale, int shared_gate, float* out, cudaStream_t stream) {
+                                 float scale, int shared_gate, float* out, int n_identity, int softmax, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || E > 1024) return fail("moe_route: %d experts (up to 1024 are taken)", E);
-    if (n_groups <= 0 || E % n_groups || keep <= 0 || keep > n_groups || top <= 0 || top > keep * (E / n_groups))
-        return fail("moe_route: %d experts in %d groups, %d kept, %d chosen", E, n_groups, keep, top);
-    const size_t bytes = (size_t)ROUTE_WARPS * 3 * E * sizeof(float);
+    const int N = E + n_identity;
+    if (E < 0 || n_identity < 0 || N <= 0 || N > 1024) return fail("moe_route: %d experts and %d identity entries (up to 1024 are taken)", E, n_identity);
+    if (n_identity > 0 && n_groups != 1) return fail("moe_route: identity entries stand in no group");
+    if (n_groups <= 0 || N % n_groups || keep <= 0 || keep > n_groups || top <= 0 || top > keep * (N / n_groups))
+        return fail("moe_route: %d entries in %d groups, %d kept, %d chosen", N, n_groups, keep, top);
+    const size_t bytes = (size_t)ROUTE_WARPS * 4 * N * sizeof(float);
     return launch_kernel("moe_route", moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
-                         bytes, stream, 1, z, correction, T, E, n_groups, keep, top, scale, shared_gate, out);
+                         bytes, stream, 1, z, correction, T, E, n_groups, keep, top, scale, shared_gate, out, n_identity, softmax);
+}
+
+JANIS_EXPORT int janis_moe_identity_add(void* out, const void* y, int dtype, const float* wts, int wts_stride, int w_col, int T,
+                                        int width, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (w_col < 0 || w_col >= wts_stride) return fail("moe_identity_add: column %d of %d", w_col, wts_stride);
+    const size_t n = (size_t)T * width;
+    if (dtype == JANIS_F32)
+        return launch_kernel("moe_identity_add", moe_identity_add_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
+                             (float*)out, (const float*)y, wts, wts_stride, w_col, width, n);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("moe_identity_add", moe_identity_add_kernel<bf16>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
+                             (bf16*)out, (const bf16*)y, wts, wts_stride, w_col, width, n);
+    return fail("moe_identity_add: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT int janis_moe_expert_act(const void* gu, int dtype, const float* wts, int E, int ff, float limit, int shared_ff,
-                                      float shared_limit, float alpha, void* out, int T, cudaStream_t stream) {
+                                      float shared_limit, float alpha, void* out, int T, int wts_stride, float up_add,
+                                      cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (wts_stride <= 0) wts_stride = E + (shared_ff ? 1 : 0);
     const size_t n = (size_t)T * ((size_t)E * ff + shared_ff);
     const int v = dtype == JANIS_F32 ? 4 : 8;
     if (ff % v == 0 && shared_ff % v == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
@@ -446,16 +498,16 @@ JANIS_EXPORT int janis_moe_expert_act(const void* gu, int dtype, const float* wt
         const dim3 grid((per_row + 255) / 256, T < 65535 ? T : 65535), block(256);
         if (dtype == JANIS_F32)
             return launch_kernel("moe_expert_act", moe_expert_act_vec_kernel<float>, grid, block, 0, stream, 1, (const float*)gu,
-                                 wts, E, ff, limit, shared_ff, shared_limit, alpha, (float*)out, T);
+                                 wts, E, ff, limit, shared_ff, shared_limit, alpha, (float*)out, T, wts_stride, up_add);
         if (dtype == JANIS_BF16)
             return launch_kernel("moe_expert_act", moe_expert_act_vec_kernel<bf16>, grid, block, 0, stream, 1, (const bf16*)gu,
-                                 wts, E, ff, limit, shared_ff, shared_limit, alpha, (bf16*)out, T);
+                                 wts, E, ff, limit, shared_ff, shared_limit, alpha, (bf16*)out, T, wts_stride, up_add);
     }
     if (dtype == JANIS_F32)
         return launch_kernel("moe_expert_act", moe_expert_act_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
-                             (const float*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (float*)out, n);
+                             (const float*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (float*)out, n, wts_stride, up_add);
     if (dtype == JANIS_BF16)
         return launch_kernel("moe_expert_act", moe_expert_act_kernel<bf16>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
-                             (const bf16*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (bf16*)out, n);
+                             (const bf16*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (bf16*)out, n, wts_stride, up_add);
     return fail("moe_expert_act: unknown dtype %d", dtype);
 }

@@ -36,7 +36,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "gemm_tc05.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_prefill_tc05.cu", "attention_no_alloc.cu"]
-MIXER_SOURCES = ["attention_talk.cu", "attention_rows.cu", "attention_prep.cu", "linear_attention.cu", "state_space.cu", "branch_ops.cu"]
+MIXER_SOURCES = ["attention_talk.cu", "attention_rows.cu", "attention_prep.cu", "linear_attention.cu", "state_space.cu", "branch_ops.cu", "hyper_streams.cu"]
 HEADERS = ["common.cuh", "attention_no_alloc.h", "attention_prefill_tiles.cuh"]
 
 

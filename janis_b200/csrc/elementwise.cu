@@ -295,6 +295,14 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
         x[i] = cap * tanhf(x[i] * inv);
 }
 
+// x *= factor in place over float values (a constant on the logits)
+__global__ void scale_values_kernel(float* __restrict__ x, size_t n, float factor) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = x[i] * factor;
+}
+
 // ---------------------------------------------------------------------------
 // rotary encoding of q and k in place, and the write of k (rotated) and v into
 // the paged cache.  qkv: [T, row_heads, hd], heads q, then k, then v (a layer that
@@ -618,6 +626,14 @@ JANIS_EXPORT int janis_softcap(float* x, long long n, float cap, cudaStream_t st
     const long long want = (n + nt - 1) / nt;
     return launch_kernel("softcap", softcap_kernel, dim3((int)(want < 148 * 32 ? want : 148 * 32)), dim3(nt), 0, stream, 1,
                          x, (size_t)n, cap);
+}
+
+JANIS_EXPORT int janis_scale_values(float* x, long long n, float factor, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int nt = 256;
+    const long long want = (n + nt - 1) / nt;
+    return launch_kernel("scale_values", scale_values_kernel, dim3((int)(want < 148 * 32 ? want : 148 * 32)), dim3(nt), 0, stream, 1,
+                         x, (size_t)n, factor);
 }
 
 JANIS_EXPORT int janis_rope_store(void* qkv, int dtype, const int* tok_pos, const int* tok_seq,

@@ -11,6 +11,7 @@
 // order and writes it back, so a prompt, a prompt that continues and a decode step are the same launch.
 #include "common.cuh"
 
+#include <math_constants.h>
 #include <type_traits>
 
 namespace janis {
@@ -212,11 +213,246 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
     }
 }
 
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]); a warp per (token, head).
+// ---------------------------------------------------------------------------
+// Matrix memory with exponential gates (mLSTM): per head and sequence a matrix C [d, dv], a vector n [d] and a
+// running maximum m, all float:
+//
+//   i_t = cap tanh((zi_t + bi) / cap),   f_t = logsigmoid(cap tanh((zf_t + bf) / cap))       (zi, zf: float logits)
+//   m_t = max(f_t + m_{t-1}, i_t)                                                               (m starts at 0)
+//   C_t = e^(f_t + m_{t-1} - m_t) C_{t-1} + e^(i_t - m_t) k_t v_t^T,   n_t likewise with k_t alone
+//   o_t = C_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
+//
+// Two kernels.  `mlstm_gates`: a warp per (sequence, head) runs the chain of maxima over the step's tokens, 32 at a
+// time, as a scan over the maps m -> max(a, b + m) (two such maps compose to one of the same form), and leaves per
+// (token, head) the three factors keep = e^(f + m' - m), take = e^(i - m), floor = e^(-m); m is loaded from and
+// written back to the cache.  `mlstm_scan`: the recurrence itself in the layout of the scan above (16 lanes a column
+// of C, each holding a run of key channels), with n as one more column whose value is 1 in every CTA (so every
+// CTA owns a copy of n: the cache keeps one per group of columns and no CTA waits for another).
+// ---------------------------------------------------------------------------
+template <int DUMMY>
+__global__ void __launch_bounds__(32)
+mlstm_gates_kernel(const float* __restrict__ z, const float* __restrict__ bias, float cap, int H,
+                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                   const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ m_state,
+                   float* __restrict__ coef) {
+    const int seq = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    grid_dependents_launch();
+    const int slot = seq_slot[seq], row0 = seq_first_row[seq], n_tok = seq_end[seq] - seq_start[seq];
+    const float bi = bias[h], bf = bias[H + h];
+    if (n_tok <= 0) return;
+    grid_dependency_wait();
+    float m = slot >= 0 ? m_state[(size_t)slot * H + h] : 0.f;
+    for (int t0 = 0; t0 < n_tok; t0 += 32) {
+        const bool in = t0 + lane < n_tok;
+        float gi = -CUDART_INF_F, gf = 0.f;                  // beyond the end: the map that changes nothing
+        if (in) {
+            const float* zr = z + (size_t)(row0 + t0 + lane) * 2 * H;
+            gi = cap * tanhf((zr[h] + bi) / cap);
+            gf = log_sigmoid(cap * tanhf((zr[H + h] + bf) / cap));
+        }
+        float a = gi, b = gf;                                // the map m -> max(a, b + m) of this token, then of all up to it
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float pa = __shfl_up_sync(0xffffffffu, a, off), pb = __shfl_up_sync(0xffffffffu, b, off);
+            if (lane >= off) {
+                a = fmaxf(a, b + pa);
+                b = b + pb;
+            }
+        }
+        const float m_new = fmaxf(a, b + m);
+        float m_prev = __shfl_up_sync(0xffffffffu, m_new, 1);
+        if (lane == 0) m_prev = m;
+        if (in) {
+            float* c = coef + ((size_t)(row0 + t0 + lane) * H + h) * 3;
+            c[0] = expf(gf + m_prev - m_new);
+            c[1] = expf(gi - m_new);
+            c[2] = expf(-m_new);
+        }
+        m = __shfl_sync(0xffffffffu, m_new, 31);
+    }
+    if (slot >= 0 && lane == 0) m_state[(size_t)slot * H + h] = m;
+}
+
+constexpr int MLSTM_GROUPS = GLA_COLS + 2;      // the value columns, the column of n, and one idle group that fills the last warp
+constexpr int MLSTM_THREADS = MLSTM_GROUPS * GLA_KS;
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(MLSTM_THREADS)
+mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__ coef,
+                  const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                  const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state_c,
+                  float* __restrict__ state_n, float* __restrict__ o_out) {
+    constexpr int RUN = DPT + 4, TOK = GLA_KS * RUN;       // floats of a lane's run, of a token
+    constexpr int TT = DPT >= 16 ? 8 : 16;                 // tokens staged per round
+    __shared__ __align__(16) float q_s[TT * TOK];
+    __shared__ __align__(16) float k_s[TT * TOK];          // k times the token's `take`
+    __shared__ float v_s[TT * GLA_COLS];
+    __shared__ float keep_s[TT], take_s[TT], floor_s[TT], nq_s[TT];
+    const int d = g.d, dv = g.dv, H = g.H;
+    const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS, n_groups = gridDim.z;
+    const int tid = threadIdx.x, ks = tid % GLA_KS, grp = tid / GLA_KS, col = col0 + grp;
+    const bool is_n = grp == GLA_COLS;                     // the column of n: its value is 1
+    const bool live = (grp < GLA_COLS && col < dv) || is_n;
+    grid_dependents_launch();
+    const int slot = seq_slot[seq], row0 = seq_first_row[seq], n_tok = seq_end[seq] - seq_start[seq];
+    if (n_tok <= 0) return;
+    grid_dependency_wait();
+    float S[DPT];
+    float* st = nullptr;
+    if (slot >= 0 && live)
+        st = is_n ? state_n + (((size_t)slot * H + h) * n_groups + blockIdx.z) * d
+                  : state_c + (((size_t)slot * H + h) * dv + col) * d;
+#pragma unroll
+    for (int ii = 0; ii < DPT; ++ii) {
+        const int i = ks * DPT + ii;
+        S[ii] = (st != nullptr && i < d) ? st[i] : 0.f;
+    }
+    constexpr int NT = GLA_COLS * GLA_KS, WIDTH = GLA_KS * DPT;       // the first NT threads stage a tile
+    constexpr int PER = TT * WIDTH / NT;
+    constexpr int CH = WIDTH / 8;
+    float qv[PER], kv[PER], vv = 0.f, cf_keep = 1.f, cf_take = 0.f, cf_floor = 1.f;
+    const bool vec = DPT >= 8 && d % 8 == 0 && g.row_elems % 8 == 0 && g.q_off % 8 == 0 && g.k_off % 8 == 0 &&
+                     (((uintptr_t)rows) & 15) == 0 && sizeof(T) == 2;
+    auto fetch = [&](int t0) {
+        if (tid < NT) {
+            if (vec) {
+#pragma unroll
+                for (int e = 0; e < PER / 8; ++e) {
+                    const int u = tid + e * NT, tt = u / CH, c0 = (u % CH) * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) qv[e * 8 + j] = kv[e * 8 + j] = 0.f;
+                    if (t0 + tt < n_tok && c0 < d) {
+                        const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                        Vec16<T>::load(row + g.q_off + h * d + c0, &qv[e * 8]);
+                        Vec16<T>::load(row + g.k_off + h * d + c0, &kv[e * 8]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    const int u = tid + e * NT;
+                    const int tt = u / WIDTH, c = u % WIDTH;
+                    qv[e] = kv[e] = 0.f;
+                    if (t0 + tt < n_tok && c < d) {
+                        const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                        qv[e] = to_float(row[g.q_off + h * d + c]);
+                        kv[e] = to_float(row[g.k_off + h * d + c]);
+                    }
+                }
+            }
+            vv = 0.f;
+            if (tid < TT * GLA_COLS) {
+                const int tt = tid / GLA_COLS, c = col0 + tid % GLA_COLS;
+                if (t0 + tt < n_tok && c < dv) vv = to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.v_off + h * dv + c]);
+            }
+        } else if (tid - NT < TT) {
+            // the tile's factors, a token a thread: keep 1, take 0 and floor 1 beyond the sequence's end change nothing
+            const int tt = tid - NT;
+            cf_keep = 1.f; cf_take = 0.f; cf_floor = 1.f;
+            if (t0 + tt < n_tok) {
+                const float* c = coef + ((size_t)(row0 + t0 + tt) * H + h) * 3;
+                cf_keep = c[0]; cf_take = c[1]; cf_floor = c[2];
+            }
+        }
+    };
+    fetch(0);
+    for (int t0 = 0; t0 < n_tok; t0 += TT) {
+        __syncthreads();                       // the tile before has been read
+        if (tid >= NT && tid - NT < TT) {
+            keep_s[tid - NT] = cf_keep;
+            take_s[tid - NT] = cf_take;
+            floor_s[tid - NT] = cf_floor;
+        }
+        __syncthreads();
+        if (tid < NT) {
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                int tt, c;
+                if (vec) {
+                    const int u = tid + (e / 8) * NT;
+                    tt = u / CH;
+                    c = (u % CH) * 8 + e % 8;
+                } else {
+                    const int u = tid + e * NT;
+                    tt = u / WIDTH;
+                    c = u % WIDTH;
+                }
+                const int at = tt * TOK + (c / DPT) * RUN + c % DPT;
+                q_s[at] = qv[e] * g.q_scale;
+                k_s[at] = kv[e] * take_s[tt];
+            }
+            if (tid < TT * GLA_COLS) v_s[tid] = vv;
+        }
+        __syncthreads();
+        if (t0 + TT < n_tok) fetch(t0 + TT);
+        float part_o[TT];
+        const int tt_n = min(TT, n_tok - t0);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            part_o[tt] = 0.f;
+            if (tt >= tt_n) continue;
+            const float v = is_n ? 1.f : (grp < GLA_COLS ? v_s[tt * GLA_COLS + grp] : 0.f);
+            const float keep = keep_s[tt];
+            const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
+            const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
+            float part[4] = {0.f, 0.f, 0.f, 0.f};           // four chains, added in a fixed order
+#pragma unroll
+            for (int i4 = 0; i4 < DPT / 4; ++i4) {
+                const float4 q4 = qq[i4], k4 = kk[i4];
+                S[4 * i4 + 0] = fmaf(keep, S[4 * i4 + 0], k4.x * v);
+                S[4 * i4 + 1] = fmaf(keep, S[4 * i4 + 1], k4.y * v);
+                S[4 * i4 + 2] = fmaf(keep, S[4 * i4 + 2], k4.z * v);
+                S[4 * i4 + 3] = fmaf(keep, S[4 * i4 + 3], k4.w * v);
+                part[0] = fmaf(S[4 * i4 + 0], q4.x, part[0]);
+                part[1] = fmaf(S[4 * i4 + 1], q4.y, part[1]);
+                part[2] = fmaf(S[4 * i4 + 2], q4.z, part[2]);
+                part[3] = fmaf(S[4 * i4 + 3], q4.w, part[3]);
+            }
+            part_o[tt] = (part[0] + part[1]) + (part[2] + part[3]);
+        }
+        // the 16 lanes of a column add their shares of all the tile's tokens at once (as in the scan above)
+        int n = TT;
+#pragma unroll
+        for (int off = GLA_KS / 2; off >= 1; off >>= 1) {
+            const bool upper = (ks & off) != 0;
+            if (n > 1) {
+                const int half = n / 2;
+#pragma unroll
+                for (int i = 0; i < TT / 2; ++i)
+                    if (i < half) {
+                        const float mine = upper ? part_o[i + half] : part_o[i];
+                        const float theirs = upper ? part_o[i] : part_o[i + half];
+                        part_o[i] = mine + __shfl_xor_sync(0xffffffffu, theirs, off);
+                    }
+                n = half;
+            } else {
+                part_o[0] += __shfl_xor_sync(0xffffffffu, part_o[0], off);
+            }
+        }
+        constexpr int SHARE = GLA_KS / TT;                  // 1, or 2 with tiles of 8 tokens
+        const int tt = ks / SHARE;
+        if (is_n && ks % SHARE == 0) nq_s[tt] = part_o[0];
+        __syncthreads();
+        if (live && !is_n && ks % SHARE == 0 && t0 + tt < n_tok)
+            o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = part_o[0] / (fmaxf(fabsf(nq_s[tt]), floor_s[tt]) + 1e-6f);
+    }
+    if (st != nullptr) {
+#pragma unroll
+        for (int ii = 0; ii < DPT; ++ii) {
+            const int i = ks * DPT + ii;
+            if (i < d) st[i] = S[ii];
+        }
+    }
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]); a warp per (token, head).  The weight is
+// one vector of dv for all heads, or (w_per_head) one of H dv with a run per head; the gate is silu or (gate_sigmoid) the
+// logistic function alone.
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ rows, int row_elems, int g_off,
-                      const float* __restrict__ w, float eps, T* __restrict__ out, int n_tok, int H, int dv) {
+                      const float* __restrict__ w, float eps, T* __restrict__ out, int n_tok, int H, int dv,
+                      int w_per_head, int gate_sigmoid) {
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     grid_dependents_launch();
     grid_dependency_wait();
@@ -229,11 +465,12 @@ head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ rows, i
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     const T* gate = rows != nullptr ? rows + (size_t)t * row_elems + g_off + h * dv : nullptr;
     T* dst = out + ((size_t)t * H + h) * dv;
+    const float* wh = w_per_head ? w + (size_t)h * dv : w;
     for (int c = lane; c < dv; c += 32) {
-        float y = src[c] * inv * w[c];
+        float y = src[c] * inv * wh[c];
         if (gate != nullptr) {
             const float gv = to_float(gate[c]);
-            y *= gv / (1.0f + expf(-gv));
+            y *= (gate_sigmoid ? 1.0f : gv) / (1.0f + expf(-gv));
         }
         dst[c] = from_float<T>(y);
     }
@@ -291,16 +528,58 @@ JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int 
     return fail("gla_scan: unknown dtype %d", dtype);
 }
 
+template <typename T>
+static int mlstm_scan_launch(const void* rows, const GlaRows& g, const float* coef, const int* seq_slot,
+                             const int* seq_first_row, const int* seq_start, const int* seq_end, float* state_c,
+                             float* state_n, float* o_out, int n_seq, cudaStream_t stream) {
+    const dim3 grid(n_seq, g.H, (g.dv + GLA_COLS - 1) / GLA_COLS), block(MLSTM_THREADS);
+#define JANIS_MLSTM_CASE(DPT)                                                                                          \
+    if (g.d <= GLA_KS * DPT)                                                                                           \
+        return launch_kernel("mlstm_scan", mlstm_scan_kernel<T, DPT>, grid, block, 0, stream, 1, (const T*)rows, g,    \
+                             coef, seq_slot, seq_first_row, seq_start, seq_end, state_c, state_n, o_out);
+    JANIS_MLSTM_CASE(4)
+    JANIS_MLSTM_CASE(8)
+    JANIS_MLSTM_CASE(16)
+#undef JANIS_MLSTM_CASE
+    return fail("mlstm_scan: key size %d is above %d", g.d, GLA_KS * 16);
+}
+
+// rows: the projected step (q [H, d], k [H, d], v [H, dv] at their offsets); z: float [n_tok, 2 H], the input gates'
+// logits then the forget gates'; bias: float [2 H]; coef: float scratch [n_tok, H, 3]; the cache parts state_c
+// [slots, H, dv, d], state_n [slots, H, ceil(dv / 8), d] and state_m [slots, H]; o_out float [n_tok, H dv].
+JANIS_EXPORT int janis_mlstm_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off,
+                                  const float* z, const float* bias, float cap, float* coef, int n_tok,
+                                  const int* seq_slot, const int* seq_first_row, const int* seq_start, const int* seq_end,
+                                  float* state_c, float* state_n, float* state_m, float* o_out, int n_seq, int H, int d,
+                                  int dv, float q_scale, cudaStream_t stream) {
+    if (n_seq <= 0 || n_tok <= 0) return 0;
+    if (H <= 0 || d <= 0 || dv <= 0) return fail("mlstm_scan: sizes %d heads, %d x %d", H, d, dv);
+    if (!(cap > 0.f)) return fail("mlstm_scan: the gates' cap must be positive");
+    if (H > 65535) return fail("mlstm_scan: too many heads (%d)", H);
+    if (launch_kernel("mlstm_gates", mlstm_gates_kernel<0>, dim3(n_seq, H), dim3(32), 0, stream, 1, z, bias, cap, H, seq_slot,
+                      seq_first_row, seq_start, seq_end, state_m, coef))
+        return 1;
+    GlaRows g;
+    g.row_elems = row_elems; g.q_off = q_off; g.k_off = k_off; g.v_off = v_off;
+    g.H = H; g.d = d; g.dv = dv; g.q_scale = q_scale; g.inv_tau = 1.0f;
+    if (dtype == JANIS_F32)
+        return mlstm_scan_launch<float>(rows, g, coef, seq_slot, seq_first_row, seq_start, seq_end, state_c, state_n, o_out, n_seq, stream);
+    if (dtype == JANIS_BF16)
+        return mlstm_scan_launch<bf16>(rows, g, coef, seq_slot, seq_first_row, seq_start, seq_end, state_c, state_n, o_out, n_seq, stream);
+    return fail("mlstm_scan: unknown dtype %d", dtype);
+}
+
 JANIS_EXPORT int janis_head_norm_gate(const float* o, const void* rows, int dtype, int row_elems, int g_off, const float* w,
-                                      float eps, void* out, int T, int H, int dv, cudaStream_t stream) {
+                                      float eps, void* out, int T, int H, int dv, int w_per_head, int gate_sigmoid,
+                                      cudaStream_t stream) {
     if (T <= 0) return 0;
     const long long units = (long long)T * H;
     const dim3 grid((unsigned)((units + 7) / 8)), block(256);
     if (dtype == JANIS_F32)
         return launch_kernel("head_norm_gate", head_norm_gate_kernel<float>, grid, block, 0, stream, 1, o, (const float*)rows,
-                             row_elems, g_off, w, eps, (float*)out, T, H, dv);
+                             row_elems, g_off, w, eps, (float*)out, T, H, dv, w_per_head, gate_sigmoid);
     if (dtype == JANIS_BF16)
         return launch_kernel("head_norm_gate", head_norm_gate_kernel<bf16>, grid, block, 0, stream, 1, o, (const bf16*)rows,
-                             row_elems, g_off, w, eps, (bf16*)out, T, H, dv);
+                             row_elems, g_off, w, eps, (bf16*)out, T, H, dv, w_per_head, gate_sigmoid);
     return fail("gla_scan: unknown dtype %d", dtype);
 }

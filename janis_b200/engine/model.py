@@ -51,6 +51,7 @@ class DecoderModel:
         self.stop_tokens = tuple(stop_tokens)
         self.max_context = int(max_context)
         self.hidden = embedding.hidden
+        self.stream_width = int(getattr(embedding, "stream_width", embedding.hidden))     # several copies of the stream side by side
         self.vocab = head.vocab
         self._check_schedule()
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.parts())
@@ -122,7 +123,7 @@ class DecoderModel:
     # -- a step ----------------------------------------------------------------
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         """Run the schedule over the step's tokens; returns the residual stream [T, hidden] float32."""
-        h = ctx.ws.buf("stream.h", (ctx.n_tok, self.hidden), torch.float32)
+        h = ctx.ws.buf("stream.h", (ctx.n_tok, self.stream_width), torch.float32)
         self.embedding.forward(ctx.tokens, ctx, h)
         y = None
         for idx, call in enumerate(self.schedule):

@@ -55,6 +55,7 @@ def core():
         lib.janis_add_rmsnorm.argtypes = [P, P, I, I, c_longlong, P, F, P, F, P, I, I, I, P]
         lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
         lib.janis_softcap.argtypes = [P, c_longlong, F, P]
+        lib.janis_scale_values.argtypes = [P, c_longlong, F, P]
         lib.janis_bias_act.argtypes = [P, P, I, I, I, I, F, F, P]
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_kv_store.argtypes = [P, I, P, P, P, P, I, I, I, I, I, P, P, P, I, I, P]
@@ -138,18 +139,20 @@ def mixers():
         lib = build.mixers_library()
         P, I, F = c_void_p, c_int, c_float
         lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
-        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, F, P, I, I, P, c_longlong, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, F, P, I, I, P, c_longlong, I, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_talk_attention_rows_floats.argtypes = [I, I, I, I, I, I, I]
         lib.janis_talk_attention_rows_floats.restype = c_longlong
         lib.janis_talk_attention_rows.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, F, P, I, P, c_longlong, P]
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
-        lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
+        lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, I, I, P]
+        lib.janis_mlstm_scan.argtypes = [P, I, I, I, I, I, P, P, F, P, I, P, P, P, P, P, P, P, P, I, I, I, I, F, P]
         lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P, I, P]
         lib.janis_conv_state_update.argtypes = [P, I, I, I, I, I, P, P, P, P, P, I, P]
         lib.janis_qkv_conv_norm_store.argtypes = [P, I, I, I, I, I, I, I, I, P, P, P, P, I, F, P, P, P, P, P, P, P, P, P, P, I, P]
-        lib.janis_latent_rotate_store.argtypes = [P, I, I, I, I, I, I, I, I, I, P, F, P, F, P, P, P, P, P, P, I, P]
+        lib.janis_latent_rotate_store.argtypes = [P, I, I, I, P, I, I, I, I, I, I, I, I, P, F, P, F, P, P, P, P, P, P, I, P]
+        lib.janis_qk_rotate_norm_store.argtypes = [P, I, I, I, I, I, I, I, I, P, I, F, P, P, P, P, P, P, I, P]
         lib.janis_head_linear.argtypes = [P, I, I, I, I, P, P, I, I, I, I, I, I, I, P]
         lib.janis_group_norm.argtypes = [P, P, I, P, F, P, F, I, P, I, I, I, P]
         lib.janis_round_rows.argtypes = [P, P, ctypes.c_size_t, P]
@@ -162,8 +165,12 @@ def mixers():
         lib.janis_dyt_norm.argtypes = [P, P, I, P, F, P, P, P, I, I, I, P]
         lib.janis_rmsnorm_accumulate.argtypes = [P, I, P, F, F, P, I, I, I, P]
         lib.janis_sigmoid_gate.argtypes = [P, P, I, I, I, I, I, I, P]
-        lib.janis_moe_route.argtypes = [P, P, I, I, I, I, I, F, I, P, P]
-        lib.janis_moe_expert_act.argtypes = [P, I, P, I, I, F, I, F, F, P, I, P]
+        lib.janis_moe_route.argtypes = [P, P, I, I, I, I, I, F, I, P, I, I, P]
+        lib.janis_moe_expert_act.argtypes = [P, I, P, I, I, F, I, F, F, P, I, I, F, P]
+        lib.janis_moe_identity_add.argtypes = [P, P, I, P, I, I, I, I, P]
+        lib.janis_hc_spread.argtypes = [P, P, I, I, I, P]
+        lib.janis_hc_read_norm.argtypes = [P, P, P, P, F, P, I, I, I, I, P]
+        lib.janis_hc_update.argtypes = [P, P, I, P, P, P, P, F, P, I, I, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
         lib.janis_mixers_set_overlap.restype = None
         lib.janis_mixers_set_overlap(1 if _overlap else 0)
@@ -460,6 +467,13 @@ def softcap(x, cap: float):
     """x = cap * tanh(x / cap) in place, float32."""
     lib = core()
     _check(lib, lib.janis_softcap(_t(x, "x", torch.float32), x.numel(), float(cap), _stream()))
+    return x
+
+
+def scale_values(x, factor: float):
+    """x *= factor in place, float32 (a constant on the logits)."""
+    lib = core()
+    _check(lib, lib.janis_scale_values(_t(x, "x", torch.float32), x.numel(), float(factor), _stream()))
     return x
 
 
@@ -812,7 +826,7 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
                    d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False,
                    max_keys: int = 0, n_chunks: int = 1, scratch=None, window: int = 0, cap: float = 0.0,
-                   sink_values=None, mix_after: bool = False, values_in_keys: bool = False, stats=None):
+                   sink_values=None, mix_after: bool = False, values_in_keys: bool = False, stats=None, keep_first: int = 0):
     """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
     own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
     alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
@@ -827,7 +841,9 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
     head h's value joins its denominator instead of 1.  mix_after: talk mixes the heads' weights after the softmax
     instead of their scores before it, which takes two passes over the keys and `stats`, float32 of at least
     `talk_attention_stats_floats` (the rows' maxima and denominators between the passes).  values_in_keys: the
-    values are the first dv features of the cached keys (vpool is not read and may be None)."""
+    values are the first dv features of the cached keys (vpool is not read and may be None).  keep_first (with a
+    window): the sequence's first `keep_first` positions stay seen behind the window, at their true positions; a bound
+    `max_keys` then counts them too."""
     T = q_rows.shape[0]
     _t(q_rows, "q_rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
@@ -854,7 +870,7 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         _t(sink_values, "sink_values", torch.float32, (H,)) if sink_values is not None else None,
         1 if mix_after else 0, 1 if values_in_keys else 0,
         _t(stats, "stats", torch.float32) if stats is not None else None, stats.numel() if stats is not None else 0,
-        _stream()),
+        int(keep_first), _stream()),
         kernels=(2 if two_pass else 1) *
                 (2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1))
     return out
@@ -942,20 +958,96 @@ def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_
     return o_out
 
 
-def head_norm_gate(o, rows, g_off: int, weight, eps: float, out, H: int, dv: int):
+def head_norm_gate(o, rows, g_off: int, weight, eps: float, out, H: int, dv: int, gate: str = "silu"):
     """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per head of dv features; the gate
-    is read from rows [T, width] at g_off (rows None: no gate).  o float32 [T, H dv], weight float32 [dv]."""
+    is read from rows [T, width] at g_off (rows None: no gate; gate="sigmoid": the logistic function alone).  o float32
+    [T, H dv]; weight float32 [dv], one vector for all heads, or [H dv] with a run per head."""
     T = o.shape[0]
+    if gate not in ("silu", "sigmoid"):
+        raise KernelError(f"head_norm_gate: unknown gate {gate!r}")
     _t(o, "o", torch.float32, (T, H * dv))
-    _t(weight, "weight", torch.float32, (dv,))
+    per_head = weight.numel() == H * dv and H > 1
+    _t(weight, "weight", torch.float32, (H * dv,) if per_head else (dv,))
     _t(out, "out", _FLOATS, (T, H * dv))
     if rows is not None:
         _t(rows, "rows", out.dtype, (T, None))
     lib = mixers()
     _check(lib, lib.janis_head_norm_gate(o.data_ptr(), rows.data_ptr() if rows is not None else None, _DT[out.dtype],
                                          rows.shape[1] if rows is not None else 0, g_off, weight.data_ptr(), float(eps),
-                                         out.data_ptr(), T, H, dv, _stream()))
+                                         out.data_ptr(), T, H, dv, 1 if per_head else 0, 1 if gate == "sigmoid" else 0,
+                                         _stream()))
     return out
+
+
+def mlstm_scan(rows, q_off: int, k_off: int, v_off: int, z, bias, cap: float, seq_slot, seq_first_row, seq_start, seq_end,
+               state_c, state_n, state_m, o_out, n_seq: int, H: int, d: int, dv: int, q_scale: float, coef):
+    """The matrix memory with exponential gates over a step's tokens, sequence by sequence in order.  rows [T, width]
+    holds q [H, d], k [H, d] and v [H, dv] at their offsets; z float32 [T, 2 H] the input gates' logits, then the forget
+    gates'; bias float32 [2 H]; with i = cap tanh((zi + bi) / cap), f = logsigmoid(cap tanh((zf + bf) / cap)):
+    m' = max(f + m, i); C <- e^(f + m - m') C + e^(i - m') k v^T; n likewise with k alone;
+    o = C^T (q q_scale) / (max(|n . q q_scale|, e^(-m')) + 1e-6).  The cache parts (float32): state_c [slots, H, dv, d]
+    (C transposed), state_n [slots, H, ceil(dv / 8), d] (a copy of n per group of 8 value columns), state_m [slots, H].
+    coef: float32 scratch [T, H, 3]; o_out float32 [T, H dv].  Sequences without a slot start from zero and store nothing."""
+    T = rows.shape[0]
+    _t(rows, "rows", _FLOATS, (T, None))
+    _t(z, "z", torch.float32, (T, 2 * H))
+    _t(bias, "bias", torch.float32, (2 * H,))
+    _t(coef, "coef", torch.float32, (T, H, 3))
+    _t(o_out, "o_out", torch.float32, (T, H * dv))
+    n_slots = state_c.shape[0]
+    _t(state_c, "state_c", torch.float32, (n_slots, H, dv, d))
+    _t(state_n, "state_n", torch.float32, (n_slots, H, (dv + 7) // 8, d))
+    _t(state_m, "state_m", torch.float32, (n_slots, H))
+    if max(q_off + H * d, k_off + H * d, v_off + H * dv) > rows.shape[1]:
+        raise KernelError("mlstm_scan: the projections do not fit the rows")
+    lib = mixers()
+    _check(lib, lib.janis_mlstm_scan(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], q_off, k_off, v_off, z.data_ptr(),
+                                     bias.data_ptr(), float(cap), coef.data_ptr(), T, _t(seq_slot, "seq_slot", torch.int32),
+                                     _t(seq_first_row, "seq_first_row", torch.int32), _t(seq_start, "seq_start", torch.int32),
+                                     _t(seq_end, "seq_end", torch.int32), state_c.data_ptr(), state_n.data_ptr(),
+                                     state_m.data_ptr(), o_out.data_ptr(), n_seq, H, d, dv, float(q_scale), _stream()),
+           kernels=2)
+    return o_out
+
+
+def hc_spread(x, h, copies: int):
+    """h[t, s] = x[t] for every copy s of the stream; x float32 [T, W], h float32 [T, copies W]."""
+    T, W = x.shape
+    lib = mixers()
+    _check(lib, lib.janis_hc_spread(_t(x, "x", torch.float32, (T, W)), _t(h, "h", torch.float32, (T, copies * W)), T,
+                                    int(copies), W, _stream()))
+    return h
+
+
+def hc_read_norm(h, copies: int, a, weight, eps: float, out, rows=None):
+    """out[r] = norm(sum_s a[s] h[row, s]) with norm(u) = u / sqrt(mean(u^2) + eps) * weight; h float32 [T, copies W],
+    a float32 [copies] (None: ones, the plain sum of the copies), weight float32 [W] (offset + w), rows: the rows to
+    read (None: all)."""
+    R, W = out.shape
+    if rows is None and h.shape[0] != R:
+        raise KernelError(f"hc_read_norm: {h.shape[0]} input rows for {R} output rows")
+    lib = mixers()
+    _check(lib, lib.janis_hc_read_norm(_t(h, "h", torch.float32, (None, copies * W)),
+                                       _t(rows, "rows", torch.int32, (R,)) if rows is not None else None,
+                                       _t(a, "a", torch.float32, (copies,)) if a is not None else None,
+                                       _t(weight, "weight", torch.float32, (W,)), float(eps), _t(out, "out", _FLOATS, (R, W)),
+                                       _DT[out.dtype], R, int(copies), W, _stream()))
+    return out
+
+
+def hc_update(h, res, copies: int, mix, b, a_next=None, w_next=None, eps_next: float = 0.0, out=None):
+    """h[t, k] <- sum_s mix[s, k] h[t, s] + b[k] res[t] for all copies k at once (float32, in place); with a_next and
+    w_next also out[t] = norm(sum_k a_next[k] h[t, k]; w_next), the next sublayer's read, in the same pass.
+    h float32 [T, copies W], res [T, W] in the activation type, mix float32 [copies, copies] ([from, to]), b [copies]."""
+    T, W = res.shape
+    fused = w_next is not None
+    lib = mixers()
+    _check(lib, lib.janis_hc_update(_t(h, "h", torch.float32, (T, copies * W)), _t(res, "res", _FLOATS, (T, W)), _DT[res.dtype],
+                                    _t(mix, "mix", torch.float32, (copies, copies)), _t(b, "b", torch.float32, (copies,)),
+                                    _t(a_next, "a_next", torch.float32, (copies,)) if fused else None,
+                                    _t(w_next, "w_next", torch.float32, (W,)) if fused else None, float(eps_next),
+                                    _t(out, "out", res.dtype, (T, W)) if fused else None, T, int(copies), W, _stream()))
+    return out if fused else None
 
 
 # ---------------------------------------------------------------------------
@@ -1172,12 +1264,14 @@ def qkv_conv_norm_store(rows, H: int, G: int, d: int, dv: int, conv_w, conv_stat
 
 
 def latent_rotate_store(rows, lat_off: int, H: int, d: int, dr: int, R: int, wc, eps: float, inv_freq, amp: float,
-                        tok_pos, tok_seq, seq_slot, qfull, kpool, page_table, rot: int | None = None):
+                        tok_pos, tok_seq, seq_slot, qfull, kpool, page_table, rot: int | None = None, q_rows=None,
+                        halves: bool = False):
     """rows [T, ...]: H query heads of d + dr at 0, the compressed row [c (R) | r (dr)] at lat_off.  c is RMS-normed with
     wc, r and every query head's last dr features are turned by the token's position (pairs 2i, 2i + 1 of the first
     `rot` of them, all when None, angle pos * inv_freq[i], sine and cosine times amp).  [norm(c) | turn(r)] becomes the key of the line's single head at the
     token's position (kpool [pages, 1, PAGE, R + dr]); the turned query parts go to qfull[t, h, R:], whose first R
-    features per head are left for the absorbed queries."""
+    features per head are left for the absorbed queries.  q_rows [T, >= H (d + dr)]: the query heads come from these rows
+    instead (a product of their own; lat_off then counts from 0 in `rows`).  halves: the turned pairs are (p, p + rot/2)."""
     T, width = rows.shape
     _t(rows, "rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
@@ -1187,12 +1281,39 @@ def latent_rotate_store(rows, lat_off: int, H: int, d: int, dr: int, R: int, wc,
         raise KernelError("latent_rotate_store: position tables shorter than the step")
     lib = mixers()
     _check(lib, lib.janis_latent_rotate_store(
-        rows.data_ptr(), _DT[rows.dtype], width, int(lat_off), T, H, d, dr, dr if rot is None else int(rot), R,
+        rows.data_ptr(), _DT[rows.dtype], width, int(lat_off),
+        _t(q_rows, "q_rows", rows.dtype, (T, None)) if q_rows is not None else None,
+        q_rows.shape[1] if q_rows is not None else 0, 1 if halves else 0, T, H, d, dr, dr if rot is None else int(rot), R,
         _t(wc, "wc", torch.float32, (R,)), float(eps), _t(inv_freq, "inv_freq", torch.float32, (dr // 2,)), float(amp),
         _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32),
         _t(qfull, "qfull", rows.dtype, (T, H * (R + dr))), kpool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         _stream()))
     return qfull
+
+
+def qk_rotate_norm_store(rows, tok_pos, tok_seq, seq_slot, inv_freq, rot: int, halves: bool, unit_norm: bool, eps: float,
+                         H: int, G: int, d: int, kpool, vpool, page_table):
+    """rows [T, >= (H + G) d]: q (H heads of d), then k (G heads).  The first `rot` features of every head turn by the
+    token's position (pairs (2p, 2p + 1), or (p, p + rot/2) with halves; angle pos * inv_freq[p]); with unit_norm every
+    head is then divided by sqrt(mean(head^2) + eps).  q is written back in place, k to the line's keys at the token's
+    position (kpool [pages, G, PAGE, d]), and k as projected to its values (vpool, the same shape; None: no values)."""
+    T = rows.shape[0]
+    _t(rows, "rows", _FLOATS, (T, None))
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", rows.dtype, (n_pages, G, PAGE, d))
+    if vpool is not None:
+        _t(vpool, "vpool", rows.dtype, (n_pages, G, PAGE, d))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("qk_rotate_norm_store: position tables shorter than the step")
+    lib = mixers()
+    _check(lib, lib.janis_qk_rotate_norm_store(
+        rows.data_ptr(), _DT[rows.dtype], rows.shape[1], T, H, G, d, int(rot), 1 if halves else 0,
+        _t(inv_freq, "inv_freq", torch.float32, (max(rot // 2, 1),)) if rot else inv_freq.data_ptr(), 1 if unit_norm else 0,
+        float(eps), _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32),
+        _t(seq_slot, "seq_slot", torch.int32), kpool.data_ptr(), vpool.data_ptr() if vpool is not None else None,
+        page_table.data_ptr(), page_table.shape[1], _stream()))
+    return rows
 
 
 HEAD_LINEAR_FEW_ROWS = 64        # up to here the kernel that keeps its rows in shared memory; above, in bfloat16, the library's batched product
@@ -1223,31 +1344,48 @@ def head_linear(x, x_head: int, x_off: int, w, out, o_head: int, o_off: int):
 
 
 def moe_route(z, correction, n_experts: int, group_count: int, group_keep: int, top: int, scale: float,
-              shared_gate: bool, out):
+              shared_gate: bool, out, n_identity: int = 0, softmax: bool = False):
     """The router's weights per token and expert, 0 for experts that were not chosen: s = sigmoid(z), choice scores
     s + correction, the best group_keep of group_count groups (by the sum of a group's two largest choice scores), the
     `top` largest choice scores among their experts, w = s / (sum of the chosen s + 1e-20) * scale.  With
-    shared_gate, column n_experts of z is a gate's logit and column n_experts of out its sigmoid.  z, out float32."""
+    shared_gate, column n_experts of z is a gate's logit and column n_experts of out its sigmoid.  z, out float32.
+    softmax: s = softmax(z) over all entries instead.  n_identity: that many more entries behind the experts in z and
+    correction (before the gate's column); they are scored and chosen like experts, and the weights of the chosen ones
+    add up in one more column at the end of out."""
     T = z.shape[0]
-    cols = n_experts + (1 if shared_gate else 0)
+    n = n_experts + n_identity
+    cols_in = n + (1 if shared_gate else 0)
+    cols_out = n_experts + (1 if shared_gate else 0) + (1 if n_identity else 0)
     lib = mixers()
-    _check(lib, lib.janis_moe_route(_t(z, "z", torch.float32, (T, cols)), _t(correction, "correction", torch.float32, (n_experts,)),
+    _check(lib, lib.janis_moe_route(_t(z, "z", torch.float32, (T, cols_in)), _t(correction, "correction", torch.float32, (n,)),
                                     T, n_experts, int(group_count), int(group_keep), int(top), float(scale),
-                                    1 if shared_gate else 0, _t(out, "out", torch.float32, (T, cols)), _stream()))
+                                    1 if shared_gate else 0, _t(out, "out", torch.float32, (T, cols_out)), int(n_identity),
+                                    1 if softmax else 0, _stream()))
     return out
 
 
-def moe_expert_act(gu, wts, n_experts: int, ff: int, limit: float, shared_ff: int, shared_limit: float, alpha: float, out):
+def moe_identity_add(out, y, wts, col: int):
+    """out[t] += wts[t, col] y[t]: what a mixture's chosen identity entries add; out, y [T, W] of one dtype, wts float32."""
+    T, W = out.shape
+    lib = mixers()
+    _check(lib, lib.janis_moe_identity_add(_t(out, "out", _FLOATS, (T, W)), _t(y, "y", out.dtype, (T, W)), _DT[out.dtype],
+                                           _t(wts, "wts", torch.float32, (T, None)), wts.shape[1], int(col), T, W, _stream()))
+    return out
+
+
+def moe_expert_act(gu, wts, n_experts: int, ff: int, limit: float, shared_ff: int, shared_limit: float, alpha: float, out,
+                   up_add: float = 1.0):
     """out[t, e * ff + j] = wts[t, e] * g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit,
     limit); gu [T, 2 (E ff + shared_ff)] holds each expert's ff gate columns followed by its ff up columns, the
-    shared expert (weight wts[t, E], its own limit) last; out [T, E ff + shared_ff]."""
+    shared expert (weight wts[t, E], its own limit) last; out [T, E ff + shared_ff].  up_add replaces the 1 (0: the plain
+    gated form); wts may have further columns behind the ones used."""
     T = gu.shape[0]
     total = n_experts * ff + shared_ff
     lib = mixers()
     _check(lib, lib.janis_moe_expert_act(_t(gu, "gu", _FLOATS, (T, 2 * total)), _DT[gu.dtype],
-                                         _t(wts, "wts", torch.float32, (T, n_experts + (1 if shared_ff else 0))),
+                                         _t(wts, "wts", torch.float32, (T, None)),
                                          n_experts, ff, float(limit), int(shared_ff), float(shared_limit), float(alpha),
-                                         _t(out, "out", gu.dtype, (T, total)), T, _stream()))
+                                         _t(out, "out", gu.dtype, (T, total)), T, wts.shape[1], float(up_add), _stream()))
     return out
 
 

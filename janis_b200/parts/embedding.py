@@ -15,8 +15,10 @@ from .base import Part, Runtime, StepContext
 
 class Embedding(Part):
     def __init__(self, vocab: int, hidden: int, table_name: str, scale: float = 1.0, init_std: float = 0.02,
-                 round_scale: bool = True):
+                 round_scale: bool = True, copies: int = 1):
         self.vocab, self.hidden = vocab, hidden
+        self.copies = int(copies)               # the stream holds this many copies of every row, side by side
+        self.stream_width = hidden * self.copies
         self.table_name = table_name
         self.scale = float(scale)
         self.round_scale = bool(round_scale)    # False: the constant multiplies as a float32 whatever the activations are
@@ -34,16 +36,22 @@ class Embedding(Part):
         self.scale_used = float(torch.tensor(self.scale, dtype=torch.float32).to(rt.dtype if self.round_scale else torch.float32))
 
     def forward(self, tokens, ctx: StepContext, out):
-        return ctx.rt.ops.embed(tokens, self.table, self.scale_used, out)
+        if self.copies == 1:
+            return ctx.rt.ops.embed(tokens, self.table, self.scale_used, out)
+        x = ctx.rt.ops.embed(tokens, self.table, self.scale_used,
+                             ctx.ws.buf("embed.x", (out.shape[0], self.hidden), torch.float32))
+        return ctx.rt.ops.hc_spread(x, out, self.copies)
 
 
 class LMHead(Part):
     """logits = y W^T, then the cap.  `table_name` may be the embedding's (a tied head)."""
 
-    def __init__(self, vocab: int, hidden: int, table_name: str, softcap: float = 0.0, init_std: float = 0.02):
+    def __init__(self, vocab: int, hidden: int, table_name: str, softcap: float = 0.0, init_std: float = 0.02,
+                 scale: float = 1.0):
         self.vocab, self.hidden = vocab, hidden
         self.table_name = table_name
         self.softcap = float(softcap or 0.0)
+        self.scale = float(scale)               # a constant on the logits (before the cap, if there is one)
         self.init_std = init_std
         self.table = None
 
@@ -55,6 +63,13 @@ class LMHead(Part):
 
     def forward(self, y, ctx: StepContext, out):
         """y [R, hidden] in the compute dtype -> out float32 [R, vocab]."""
+        if self.scale != 1.0:
+            if self.softcap > 0:
+                raise NotImplementedError("a constant on the logits together with a cap")
+            return ctx.rt.ops.scale_values(self._product(y, ctx, out), self.scale)
+        return self._product(y, ctx, out)
+
+    def _product(self, y, ctx: StepContext, out):
         ops = ctx.rt.ops
         R = y.shape[0]
         if ctx.rt.dtype == torch.float32:

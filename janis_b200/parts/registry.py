@@ -43,6 +43,8 @@ def _register_builtin() -> None:
     from .embedding import Embedding, LMHead
     from .feedforward import DenseMLP, GatedMLP
     from .filtered_attention import FilteredAttention
+    from .hyper import HyperConnectionBlock, HyperRead
+    from .matrix_memory import MatrixMemory
     from .latent_attention import LatentAttention
     from .linear_attention import GatedLinearAttention
     from .talking_attention import TalkingHeadsAttention
@@ -57,6 +59,7 @@ def _register_builtin() -> None:
     register("mixer", "filtered_attention", FilteredAttention)             # filtered and normed projections, capped scores, weights mixed after the softmax
     register("mixer", "latent_attention", LatentAttention)                 # one compressed row cached per position, a sink per head, a window
     register("mixer", "gated_linear_attention", GatedLinearAttention)     # a matrix of state per head, decays per key channel
+    register("mixer", "matrix_memory", MatrixMemory)                      # a matrix, a normaliser and a running maximum per head, exponential gates
     register("mixer", "selective_scan", SelectiveScanMixer)               # a state per channel, step sizes through a low rank
     register("mixer", "state_space_duality", DualityMixer)                # a scalar decay per head, grouped B and C
     register("mixer", "parallel", ParallelMixers)                         # branches on one input, normed and averaged
@@ -66,11 +69,13 @@ def _register_builtin() -> None:
     register("norm", "rms_norm", RMSNorm)
     register("norm", "dynamic_tanh", DynamicTanh)
     register("norm", "group_rms_norm", GroupRMSNorm)       # each run of the row by its own root mean square; norms the stream in place
+    register("norm", "hyper_read", HyperRead)              # a weighted sum of the stream's copies, then the RMS norm
     register("position", "rotary", RotaryEncoding)
     register("position", "none", NoPosition)
     register("block", "sandwich", SandwichBlock)
     register("block", "pre_norm", PreNormBlock)
     register("block", "post_norm", PostNormBlock)          # the norm after the sum, the stream scaled by a constant
+    register("block", "hyper_connections", HyperConnectionBlock)   # copies of the stream read and written through small stored maps
     register("embedding", "scaled_table", Embedding)       # rows of a table times a constant (1 for most models)
     register("head", "capped_linear", LMHead)              # y W^T, tied to the embedding's table or not, then an optional cap
 

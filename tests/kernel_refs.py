@@ -355,7 +355,7 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G,
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
                    block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None, window=0, cap=0.0,
-                   sink_values=None, mix_after=False, values_in_keys=False, stats=None):
+                   sink_values=None, mix_after=False, values_in_keys=False, stats=None, keep_first=0):
     T = q_rows.shape[0]
     rep = H // G
     for t in range(T):
@@ -366,7 +366,7 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         first = (pos // block) * block if block > 0 else 0
         if window > 0:
             first = max(first, pos - window + 1)
-        js = list(range(first, pos + 1))
+        js = list(range(min(keep_first, first) if window > 0 else 0)) + list(range(first, pos + 1))
         pages = [int(page_table[slot, j // PAGE]) for j in js]
         k = torch.stack([kpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, d]
         v = k[..., :dv] if values_in_keys else torch.stack([vpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()
@@ -429,13 +429,14 @@ def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_
     return o_out
 
 
-def head_norm_gate(o, rows, g_off, weight, eps, out, H, dv):
+def head_norm_gate(o, rows, g_off, weight, eps, out, H, dv, gate="silu"):
     T = o.shape[0]
     x = o.double().view(T, H, dv)
-    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+    w = weight.double().view(H, dv) if weight.numel() == H * dv and H > 1 else weight.double()
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
     if rows is not None:
         g = rows[:, g_off:g_off + H * dv].double().view(T, H, dv)
-        y = y * g * torch.sigmoid(g)
+        y = y * torch.sigmoid(g) * (g if gate == "silu" else 1.0)
     out.copy_(y.reshape(T, H * dv).to(out.dtype))
     return out
 
@@ -593,7 +594,7 @@ def qkv_conv_norm_store(rows, H, G, d, dv, conv_w, conv_state, wq, wk, v_unit, e
 
 
 def latent_rotate_store(rows, lat_off, H, d, dr, R, wc, eps, inv_freq, amp, tok_pos, tok_seq, seq_slot, qfull, kpool,
-                        page_table, rot=None):
+                        page_table, rot=None, q_rows=None, halves=False):
     T = rows.shape[0]
     D = R + dr
     for t in range(T):
@@ -604,13 +605,20 @@ def latent_rotate_store(rows, lat_off, H, d, dr, R, wc, eps, inv_freq, amp, tok_
             cs[rot // 2:], sn[rot // 2:] = 1.0, 0.0
 
         def turn(x):
+            if halves:
+                w = dr if rot is None else rot
+                a, b = x[..., :w // 2], x[..., w // 2:w]
+                out = x.clone()
+                out[..., :w // 2] = a * cs[:w // 2] - b * sn[:w // 2]
+                out[..., w // 2:w] = b * cs[:w // 2] + a * sn[:w // 2]
+                return out
             a, b = x[..., 0::2], x[..., 1::2]
             out = torch.empty_like(x)
             out[..., 0::2] = a * cs - b * sn
             out[..., 1::2] = b * cs + a * sn
             return out
         row = rows[t].double()
-        q = row[:H * (d + dr)].view(H, d + dr)
+        q = (q_rows[t].double() if q_rows is not None else row)[:H * (d + dr)].view(H, d + dr)
         qfull.view(T, H, D)[t, :, R:] = turn(q[:, d:]).to(qfull.dtype)
         if slot < 0:
             continue
@@ -630,9 +638,11 @@ def head_linear(x, x_head, x_off, w, out, o_head, o_off):
     return out
 
 
-def moe_route(z, correction, n_experts, group_count, group_keep, top, scale, shared_gate, out):
+def moe_route(z, correction, n_experts, group_count, group_keep, top, scale, shared_gate, out, n_identity=0, softmax=False):
     T = z.shape[0]
-    s = torch.sigmoid(z[:, :n_experts].double())
+    real = n_experts
+    n_experts = real + n_identity          # the entries that are scored and chosen
+    s = torch.softmax(z[:, :n_experts].double(), -1) if softmax else torch.sigmoid(z[:, :n_experts].double())
     c = s + correction.double()
     per = n_experts // group_count
     out.zero_()
@@ -643,22 +653,129 @@ def moe_route(z, correction, n_experts, group_count, group_keep, top, scale, sha
         chosen = sorted(cand, key=lambda e: (-float(c[t, e]), e))[:top]
         total = sum(float(s[t, e]) for e in chosen) + 1e-20
         for e in chosen:
-            out[t, e] = float(s[t, e]) / total * scale
+            if e < real:
+                out[t, e] = float(s[t, e]) / total * scale
+            else:
+                out[t, -1] += float(s[t, e]) / total * scale
     if shared_gate:
-        out[:, n_experts] = torch.sigmoid(z[:, n_experts].double()).float()
+        out[:, real] = torch.sigmoid(z[:, n_experts].double()).float()
     return out
 
 
-def moe_expert_act(gu, wts, n_experts, ff, limit, shared_ff, shared_limit, alpha, out):
+def moe_identity_add(out, y, wts, col):
+    out.copy_((out.double() + wts[:, col:col + 1].double() * y.double()).to(out.dtype))
+    return out
+
+
+def moe_expert_act(gu, wts, n_experts, ff, limit, shared_ff, shared_limit, alpha, out, up_add=1.0):
     T = gu.shape[0]
     v = gu.double()
     E = n_experts
     g = v[:, :2 * E * ff].view(T, E, 2, ff)
     gate, up = torch.clamp(g[:, :, 0], max=limit), torch.clamp(g[:, :, 1], min=-limit, max=limit)
-    a = gate * torch.sigmoid(alpha * gate) * (up + 1.0) * wts[:, :E].double()[:, :, None]
+    a = gate * torch.sigmoid(alpha * gate) * (up + up_add) * wts[:, :E].double()[:, :, None]
     out[:, :E * ff] = a.reshape(T, E * ff).to(out.dtype)
     if shared_ff:
         sg = v[:, 2 * E * ff:].view(T, 2, shared_ff)
         gate, up = torch.clamp(sg[:, 0], max=shared_limit), torch.clamp(sg[:, 1], min=-shared_limit, max=shared_limit)
-        out[:, E * ff:] = (gate * torch.sigmoid(alpha * gate) * (up + 1.0) * wts[:, E:E + 1].double()).to(out.dtype)
+        out[:, E * ff:] = (gate * torch.sigmoid(alpha * gate) * (up + up_add) * wts[:, E:E + 1].double()).to(out.dtype)
     return out
+
+
+# ---------------------------------------------------------------------------
+# copies of the stream behind small maps, queries and keys turned and normed, the matrix memory, a constant on logits
+# ---------------------------------------------------------------------------
+
+def scale_values(x, factor):
+    x.mul_(factor)
+    return x
+
+
+def hc_spread(x, h, copies):
+    T, W = x.shape
+    h.view(T, copies, W).copy_(x[:, None, :].expand(T, copies, W))
+    return h
+
+
+def hc_read_norm(h, copies, a, weight, eps, out, rows=None):
+    R, W = out.shape
+    x = h.double().view(-1, copies, W)
+    if rows is not None:
+        x = x[rows.long()]
+    av = a.double() if a is not None else torch.ones(copies, dtype=torch.float64)
+    u = (x * av[None, :, None]).sum(1)
+    out.copy_((u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * weight.double()).to(out.dtype))
+    return out
+
+
+def hc_update(h, res, copies, mix, b, a_next=None, w_next=None, eps_next=0.0, out=None):
+    T, W = res.shape
+    x = h.double().view(T, copies, W)
+    new = torch.einsum("sk,tsw->tkw", mix.double(), x) + b.double()[None, :, None] * res.double()[:, None, :]
+    h.copy_(new.reshape(T, copies * W).float())
+    if w_next is None:
+        return None
+    return hc_read_norm(h, copies, a_next, w_next, eps_next, out)
+
+
+def qk_rotate_norm_store(rows, tok_pos, tok_seq, seq_slot, inv_freq, rot, halves, unit_norm, eps, H, G, d, kpool, vpool,
+                         page_table):
+    T = rows.shape[0]
+    for t in range(T):
+        pos, slot = int(tok_pos[t]), int(seq_slot[int(tok_seq[t])])
+        heads = rows[t, :(H + G) * d].double().view(H + G, d)
+        raw_k = heads[H:].clone()
+        y = heads.clone()
+        if rot:
+            ang = float(np.float32(pos)) * inv_freq.double()[:rot // 2]
+            cs, sn = torch.cos(ang), torch.sin(ang)
+            if halves:
+                a, b = heads[:, :rot // 2], heads[:, rot // 2:rot]
+                y[:, :rot // 2], y[:, rot // 2:rot] = a * cs - b * sn, b * cs + a * sn
+            else:
+                a, b = heads[:, 0:rot:2], heads[:, 1:rot:2]
+                y[:, 0:rot:2], y[:, 1:rot:2] = a * cs - b * sn, b * cs + a * sn
+        if unit_norm:
+            y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+        rows[t, :H * d] = y[:H].reshape(-1).to(rows.dtype)
+        if slot < 0:
+            continue
+        page = int(page_table[slot, pos // PAGE])
+        kpool[page, :, pos % PAGE] = y[H:].to(kpool.dtype)
+        if vpool is not None:
+            vpool[page, :, pos % PAGE] = raw_k.to(vpool.dtype)
+    return rows
+
+
+def mlstm_scan(rows, q_off, k_off, v_off, z, bias, cap, seq_slot, seq_first_row, seq_start, seq_end, state_c, state_n,
+               state_m, o_out, n_seq, H, d, dv, q_scale, coef):
+    for s in range(n_seq):
+        slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
+        if n <= 0:
+            continue
+        if slot >= 0:
+            C = state_c[slot].double().transpose(1, 2).clone()       # stored [H, dv, d]
+            nn = state_n[slot, :, 0].double().clone()
+            m = state_m[slot].double().clone()
+        else:
+            C, nn, m = torch.zeros(H, d, dv, dtype=torch.float64), torch.zeros(H, d, dtype=torch.float64), torch.zeros(H, dtype=torch.float64)
+        for t in range(row0, row0 + n):
+            row = rows[t].double()
+            q = row[q_off:q_off + H * d].view(H, d) * q_scale
+            k = row[k_off:k_off + H * d].view(H, d)
+            v = row[v_off:v_off + H * dv].view(H, dv)
+            zz = z[t].double() + bias.double()
+            gi = cap * torch.tanh(zz[:H] / cap)
+            gf = torch.nn.functional.logsigmoid(cap * torch.tanh(zz[H:] / cap))
+            m_new = torch.maximum(gf + m, gi)
+            keep, take = torch.exp(gf + m - m_new), torch.exp(gi - m_new)
+            C = keep[:, None, None] * C + take[:, None, None] * k[:, :, None] * v[:, None, :]
+            nn = keep[:, None] * nn + take[:, None] * k
+            m = m_new
+            den = torch.maximum((nn * q).sum(-1).abs(), torch.exp(-m)) + 1e-6
+            o_out[t] = (torch.einsum("hdv,hd->hv", C, q) / den[:, None]).reshape(-1).float()
+        if slot >= 0:
+            state_c[slot] = C.transpose(1, 2).float()
+            state_n[slot] = nn.float()[:, None, :].expand(H, state_n.shape[2], d)
+            state_m[slot] = m.float()
+    return o_out
