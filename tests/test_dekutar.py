@@ -1,0 +1,777 @@
+"""Dekutar: each mechanism against its plain statement, and the engine against the plain model.
+
+The configurations are small and differ from each other in every size and option: two, three and one copy of the
+stream and the plain residual sum; every order of the three mixers; grouped and ungrouped heads; rotated parts of two
+features, of part of the head and of the whole head; windows of one position, of no whole page and of two whole pages
+with none, one and several kept first positions, and no window; compressed rows that are no multiple of anything;
+matrix memories with more value than key channels and the reverse; routers with and without identity entries and
+shared experts, one expert chosen and several; layers without a feed-forward; widths that are no multiple of 8.
+Weights are seeded random ones with the projections of queries and keys scaled up, so that the attention weights are
+far from uniform, and gate biases spread, so that some heads of the matrix memory forget within a few tokens and
+others remember hundreds.  The bfloat16 cases read folders whose routers are steep and whose corrections are well
+apart: a close call that rounding decides the other way is another row of logits, not a rounding.
+
+Engine cases run on the GPU (`-m gpu`, float32 and bfloat16) and, as a check of the host side alone, on the CPU over
+the plain kernel statements (float32, shorter requests).
+"""
+from __future__ import annotations
+
+import copy
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests.conftest import random_tokens
+from tests.helpers import assert_logits as _assert_exact, make_engine, run_in_pieces, run_requests
+
+GPU = pytest.mark.gpu
+CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloat16", marks=GPU),
+         pytest.param("refs", "float32")]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def assert_logits(got, want, dtype, what):
+    """float32: every logit within 1e-4 of the largest one.  bfloat16: rows are judged by the root mean square of
+    their difference against that of the logits: 96 in 100 (or all but two) within 5 %, at most two beyond 12 % (a
+    router's close call that the rounding decides the other way), half of them within 1.5 %."""
+    if dtype in ("float32", torch.float32):
+        return _assert_exact(got, want, dtype, what)
+    got, want = got.detach().double().cpu(), want.double().cpu()
+    assert got.shape == want.shape and torch.isfinite(got).all(), what
+    rows = (got - want).pow(2).mean(1).sqrt() / want.pow(2).mean().sqrt()
+    n = rows.numel()
+    bad, worse = int((rows > 5e-2).sum()), int((rows > 12e-2).sum())
+    assert bad <= max(2, n // 25) and worse <= 2 and rows.median().item() < 1.5e-2, \
+        f"{what}: {bad} of {n} rows beyond 5 %, {worse} beyond 12 %, worst {rows.max().item():.3f} at {int(rows.argmax())}, median {rows.median().item():.4f}"
+
+
+def _lat(heads, dim, rot_dim, vdim, rank, q_rank, scale, base=10000.0):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "q_rank": q_rank, "scale": scale,
+            "rot": {"base": base, "dims": rot_dim}}
+
+
+def _att(heads, kv, dim, scale, rot=0, base=10000.0, window=0, keep=0):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": scale}
+    if rot:
+        m["rot"] = {"base": base, "dims": rot}
+    if window:
+        m["mask"] = {"size": window, "keep_first": keep}
+    return m
+
+
+def _mem(heads, dim, vdim, cap):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
+
+
+def _moe(experts, identity, top, ff, shared=0):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": identity, "top": top},
+            "shared": {"ff": shared} if shared else None}
+
+
+def _model(vocab, width, streams, eps, emb, logit, layers):
+    d = {"architecture": "Dekutar", "vocab": vocab, "width": width, "embedding": {"scale": emb}, "norm": {"eps": eps},
+         "logit_scale": logit, "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+    if streams:
+        d["streams"] = streams
+    return d
+
+
+# two copies; a window that is no whole page with three kept positions; part of the head turned; identity entries
+DEK_A = _model(200, 64, 2, 1e-6, 8.0, 2.0, [
+    ("latent_attention", _lat(4, 16, 8, 16, 24, 40, 0.2, base=1000.0), _moe(6, 2, 3, 24, shared=40)),
+    ("attention", _att(4, 1, 16, 0.25, rot=8, base=100.0, window=24, keep=3), _moe(6, 2, 3, 24, shared=40)),
+    ("mlstm", _mem(2, 16, 24, 15.0), _moe(6, 2, 3, 24, shared=40)),
+    ("latent_attention", _lat(2, 8, 16, 24, 32, 16, 0.2, base=50000.0), None)])
+
+# three copies; the matrix memory first; as many key/value heads as heads; a window without kept positions and no
+# window; the whole head turned; no identity entries, no shared expert, one expert chosen
+DEK_B = _model(333, 96, 3, 1e-5, 1.0, 0.5, [
+    ("mlstm", _mem(3, 32, 16, 8.0), _moe(4, 0, 1, 32)),
+    ("attention", _att(6, 6, 16, 0.3, rot=16, base=500.0, window=70), None),
+    ("latent_attention", _lat(3, 32, 16, 40, 48, 24, 0.15, base=500.0), _moe(5, 3, 2, 16, shared=16)),
+    ("attention", _att(2, 1, 32, 0.2, rot=2), _moe(4, 0, 1, 32))])
+
+# the plain residual sum; sizes a tensor-core kernel takes; a window of two whole pages with eight kept positions
+DEK_C = _model(512, 128, 0, 1e-6, 12.0, 1.0, [
+    ("attention", _att(8, 2, 64, 0.12, rot=32, base=300000.0, window=128, keep=8), _moe(8, 4, 4, 64, shared=96)),
+    ("latent_attention", _lat(8, 32, 32, 32, 96, 64, 0.12, base=300000.0), _moe(8, 4, 4, 64, shared=96)),
+    ("mlstm", _mem(4, 64, 64, 15.0), None),
+    ("attention", _att(16, 16, 16, 0.25, rot=16, window=64, keep=1), _moe(16, 0, 2, 32))])
+
+# one copy behind its maps; sizes that are multiples of little; a window of five with one kept position and a window of
+# one position with two; a rotated part of two features; all router entries but one are identity entries
+DEK_D = _model(301, 72, 1, 1e-4, 3.0, 1.5, [
+    ("attention", _att(5, 5, 10, 0.3, rot=4, window=5, keep=1), _moe(3, 1, 1, 21)),
+    ("latent_attention", _lat(3, 12, 6, 14, 10, 9, 0.3, base=100.0), _moe(1, 3, 2, 21, shared=13)),
+    ("mlstm", _mem(5, 10, 6, 4.0), None),
+    ("attention", _att(3, 1, 6, 0.4, window=1, keep=2), None),
+    ("latent_attention", _lat(1, 6, 2, 6, 7, 5, 0.4, base=100.0), _moe(3, 1, 1, 21))])
+
+# each mixer alone, without a feed-forward; a width that is no multiple of 8
+DEK_E = _model(150, 48, 2, 1e-6, 1.0, 1.0, [("mlstm", _mem(3, 16, 16, 10.0), None)])
+DEK_F = _model(97, 36, 4, 1e-5, 2.0, 3.0, [("attention", _att(2, 1, 12, 0.3, rot=12, window=9, keep=2), None),
+                                          ("latent_attention", _lat(2, 4, 4, 6, 12, 6, 0.3), _moe(2, 1, 2, 18))])
+
+DEK = {"A": DEK_A, "B": DEK_B, "C": DEK_C, "D": DEK_D, "E": DEK_E, "F": DEK_F}
+
+
+def write_dekutar(model_dir: str, raw: dict, seed: int, steep_router: bool = False, gain: float = 3.0, qk_gain: float = 6.0,
+                  router_gain: float = 20.0) -> None:
+    """A folder of seeded random weights: query and key projections scaled up (peaked attention weights); the gates'
+    biases of the matrix memory spread; the output side of every sublayer scaled up so that the sublayers weigh
+    against the stream; with steep_router the routers' rows are scaled up and the corrections are distinct steps with a
+    jitter.  The gains suit widths of a hundred."""
+    from janis_b200 import build_model
+    from janis_b200.weights.loader import random_tensors, write_model_folder
+    _, cfg, model = build_model(raw)
+    tensors = random_tensors(model.tensor_specs(), seed, "cpu")
+    kinds = {f"l{i}": l["type"] for i, l in enumerate(raw["layers"])}
+    for name, t in list(tensors.items()):
+        layer = name.split(".")[0]
+        g = torch.Generator().manual_seed(seed + len(name))
+        if kinds.get(layer) in ("attention", "latent_attention") and name.endswith((".mix.q", ".mix.k", ".mix.uq", ".mix.uk")):
+            tensors[name] = (t.float() * qk_gain).to(torch.bfloat16)
+        elif name.endswith(".mix.f.b"):
+            tensors[name] = torch.linspace(-1.0, 6.0, t.numel())[torch.randperm(t.numel(), generator=g)].to(torch.bfloat16)
+        elif name.endswith(".mix.i.b"):
+            tensors[name] = (2.0 * torch.randn(t.numel(), generator=g)).to(torch.bfloat16)
+        elif name.endswith((".mix.i", ".mix.f")):
+            tensors[name] = (t.float() * 10.0).to(torch.bfloat16)
+        elif name.endswith(".mlp.router"):
+            tensors[name] = (t.float() * router_gain * (40.0 if steep_router else 1.0)).to(torch.bfloat16)
+        elif name.endswith(".mlp.correction") and steep_router:
+            n = t.numel()
+            tensors[name] = (0.07 * torch.randperm(n, generator=g).float() + 0.03 * torch.rand(n, generator=g)).to(torch.bfloat16)
+        elif name.endswith((".o", ".down", ".up", ".gate", ".mix.g", ".mix.v", ".mix.dkv", ".mix.dq", ".mix.uv")):
+            tensors[name] = (t.float() * gain).to(torch.bfloat16)
+    write_model_folder(model_dir, cfg.to_dict(), tensors, {"seed": str(seed)})
+
+
+@pytest.fixture(scope="module")
+def dek_dirs(tmp_path_factory):
+    out = {}
+    for i, (key, raw) in enumerate(DEK.items()):
+        for steep in (False, True):
+            d = tmp_path_factory.mktemp(f"dekutar_{key}{'_steep' if steep else ''}")
+            write_dekutar(str(d), raw, 700 + i, steep)
+            out[(key, steep)] = str(d)
+    return out
+
+
+@pytest.fixture(scope="module")
+def plain(dek_dirs):
+    from tests.plain import dekutar_plain as P
+    loaded, memo = {}, {}
+
+    def logits(key, steep, tokens):
+        if (key, steep) not in loaded:
+            loaded[(key, steep)] = P.load_folder(dek_dirs[(key, steep)])
+        k = (key, steep, tuple(tokens))
+        if k not in memo:
+            cfg, w = loaded[(key, steep)]
+            memo[k] = P.forward(cfg, w, list(tokens))
+        return memo[k]
+
+    return logits
+
+
+@pytest.fixture(scope="module")
+def engines(dek_dirs):
+    made = {}
+
+    def get(key, dtype, on, **kw):
+        steep = dtype == "bfloat16"
+        k = (key, dtype, on, tuple(sorted(kw.items())))
+        if k not in made:
+            made[k] = make_engine(dek_dirs[(key, steep)], dtype, on, **kw)
+        return made[k], steep
+
+    yield get
+    for e in made.values():
+        e.close()
+
+
+def keys_for(on):
+    return list(DEK) if on == "cuda" else ["A", "B", "D", "E", "F"]
+
+
+def _requests(vocab, lens, seed):
+    return [random_tokens(vocab, n, seed + i) for i, n in enumerate(lens)]
+
+
+# ---------------------------------------------------------------------------
+# configuration and registry
+# ---------------------------------------------------------------------------
+
+def test_configuration_reads_back_and_guards():
+    from janis_b200 import ConfigError, DekutarConfig, build_model, resolve
+    cfg = DekutarConfig.from_dict(DEK_A)
+    assert DekutarConfig.from_dict(cfg.to_dict()) == cfg
+    assert resolve(DEK_A).name == "Dekutar"
+    assert cfg.streams == 2 and cfg.logit_scale == 2.0 and cfg.embedding_scale == 8.0
+    assert cfg.layers[1].mixer.window == 24 and cfg.layers[1].mixer.keep_first == 3 and cfg.layers[1].mixer.rot_dims == 8
+    assert cfg.layers[3].mlp is None and cfg.layers[0].mlp.identity == 2 and cfg.layers[0].mlp.shared_ff == 40
+    assert DekutarConfig.from_dict(DEK_C).streams == 0
+    _, _, model = build_model(DEK_A)
+    specs = model.tensor_specs()
+    assert specs["l0.mix.dq"].shape == (40, 64) and specs["l0.mix.uq"].shape == (4 * 24, 40) and specs["l0.mix.dkv"].shape == (32, 64)
+    assert specs["l0.mix.g"].shape == (64, 64) and specs["l1.mix.g"].shape == (4, 64) and specs["l1.mix.k"].shape == (16, 64)
+    assert "l1.mix.v" not in specs and "l0.mix.q" not in specs and "l0.mix.sink" not in specs and "l3.norm2" not in specs
+    assert specs["l0.mlp.router"].shape == (8, 64) and specs["l0.mlp.correction"].shape == (8,) and "l0.mlp.e6.gate" not in specs
+    assert specs["l0.hc1.mix"].shape == (2, 2) and specs["l0.hc2.in"].shape == (2,) and "l3.hc2.in" not in specs
+    assert specs["l2.mix.i.b"].shape == (2,) and specs["l2.mix.norm"].shape == (48,)
+    needs = model.cache_line_needs()
+    assert set(needs[0]) == {"kv"} and needs[0]["kv"].n_kv_heads == 1 and needs[0]["kv"].head_dim == 32
+    assert needs[1]["kv"].n_kv_heads == 1 and needs[1]["kv"].value_dim == 16
+    assert set(needs[2]) == {"memory", "normaliser", "maximum"} and needs[2]["memory"].shape == (2, 24, 16)
+    _, _, plain_model = build_model(DEK_C)
+    assert "l0.hc1.in" not in plain_model.tensor_specs() and plain_model.stream_width == 128 and model.stream_width == 128
+    bad_layers = [
+        [{"type": "conv", "mixer": {}, "mlp": None}],
+        [{"type": "attention", "mixer": _att(4, 3, 32, 0.2), "mlp": None}],
+        [{"type": "attention", "mixer": {**_att(4, 2, 32, 0.2), "vdim": 16}, "mlp": None}],
+        [{"type": "attention", "mixer": _att(4, 2, 32, 0.2, rot=34), "mlp": None}],
+        [{"type": "latent_attention", "mixer": _lat(4, 16, 7, 16, 24, 8, 0.2), "mlp": None}],
+        [{"type": "mlstm", "mixer": _mem(2, 8, 8, 0.0), "mlp": None}],
+        [{"type": "mlstm", "mixer": _mem(2, 8, 8, 5.0), "mlp": _moe(2, 1, 4, 8)}],
+        [{"type": "mlstm", "mixer": _mem(2, 8, 8, 5.0), "mlp": {**_moe(2, 1, 1, 8), "kind": "dense"}}]]
+    for layers in bad_layers:
+        with pytest.raises(ConfigError):
+            DekutarConfig.from_dict({**DEK_A, "layers": layers})
+    with pytest.raises(ConfigError):
+        DekutarConfig.from_dict({**DEK_A, "streams": 9})
+
+
+# ---------------------------------------------------------------------------
+# the plain statements by hand
+# ---------------------------------------------------------------------------
+
+def test_plain_turns_window_and_router_by_hand():
+    from tests.plain import dekutar_plain as P
+    x = torch.tensor([[[1.0, 0.0, 0.0, 1.0, 5.0]]], dtype=torch.float64).repeat(2, 1, 1)
+    pos = torch.arange(2)
+    # base 1: every pair turns by the position itself; position 0 changes nothing
+    near = P.turn_neighbours(x, pos, 1.0, 4)
+    c, s = math.cos(1.0), math.sin(1.0)
+    assert torch.equal(near[0], x[0])
+    assert torch.allclose(near[1, 0], torch.tensor([c, s, -s, c, 5.0], dtype=torch.float64))       # pairs (0, 1) and (2, 3)
+    half = P.turn_halves(x, pos, 1.0, 4)
+    assert torch.allclose(half[1, 0], torch.tensor([c, -s, s, c, 5.0], dtype=torch.float64))       # pairs (0, 2) and (1, 3)
+    seen = P.window_seen(3, 2)
+    assert [j for j in range(8) if seen(7, j)] == [0, 1, 5, 6, 7] and [j for j in range(4) if seen(3, j)] == [0, 1, 2, 3]
+    assert [j for j in range(8) if P.window_seen(0, 0)(7, j)] == list(range(8))
+    # the router: softmax over all entries; the correction chooses, the scores weigh
+    z = torch.log(torch.tensor([[0.1, 0.2, 0.3, 0.4]], dtype=torch.float64))
+    chosen, w = P.route(z, torch.tensor([0.5, 0.0, 0.0, 0.0], dtype=torch.float64), 2)
+    assert sorted(chosen[0].tolist()) == [0, 3]
+    got = dict(zip(chosen[0].tolist(), w[0].tolist()))
+    assert abs(got[0] - 0.2) < 1e-12 and abs(got[3] - 0.8) < 1e-12
+    # identity entries return the input: one expert of zeros and one identity entry, both chosen
+    t = {"m.router": torch.tensor([[0.0, 0.0], [0.0, 0.0]], dtype=torch.float64), "m.correction": torch.zeros(2, dtype=torch.float64),
+         "m.e0.gate": torch.zeros(3, 2, dtype=torch.float64), "m.e0.up": torch.zeros(3, 2, dtype=torch.float64),
+         "m.e0.down": torch.zeros(2, 3, dtype=torch.float64)}
+    y = torch.tensor([[2.0, -4.0]], dtype=torch.float64)
+    out = P.experts(y, t, "m", {"router": {"experts": 1, "identity": 1, "top": 2}, "shared": None})
+    assert torch.allclose(out, 0.5 * y)
+
+
+def test_plain_matrix_memory_and_streams_by_hand():
+    from tests.plain import dekutar_plain as P
+    # one head, d = dv = 1, every projection the input itself, gates without weights: i = cap tanh(b_i / cap), f likewise
+    W = 1
+    t = {k: torch.ones(1, W, dtype=torch.float64) for k in ("m.q", "m.k", "m.v", "m.o")}
+    t.update({"m.i": torch.zeros(1, W, dtype=torch.float64), "m.f": torch.zeros(1, W, dtype=torch.float64),
+              "m.i.b": torch.tensor([1.0], dtype=torch.float64), "m.f.b": torch.tensor([0.0], dtype=torch.float64),
+              "m.g": torch.zeros(1, W, dtype=torch.float64), "m.norm": torch.ones(1, dtype=torch.float64)})
+    cap = 50.0
+    y = torch.tensor([[2.0], [3.0]], dtype=torch.float64)
+    out = P.mlstm(y, t, "m", {"heads": 1, "dim": 1, "vdim": 1, "gate_cap": cap}, 0.0)
+    # one channel: the head norm leaves the sign, the gate is 1/2
+    assert torch.allclose(out, torch.tensor([[0.5], [0.5]], dtype=torch.float64))
+    # the same by hand up to the norm: m starts at 0
+    gi = cap * math.tanh(1.0 / cap)
+    gf = math.log(0.5)
+    m1 = max(gf + 0.0, gi)
+    C1, n1 = math.exp(gi - m1) * 4.0, math.exp(gi - m1) * 2.0
+    o1 = C1 * 2.0 / (max(abs(n1 * 2.0), math.exp(-m1)) + 1e-6)
+    m2 = max(gf + m1, gi)
+    C2 = math.exp(gf + m1 - m2) * C1 + math.exp(gi - m2) * 9.0
+    n2 = math.exp(gf + m1 - m2) * n1 + math.exp(gi - m2) * 3.0
+    o2 = C2 * 3.0 / (max(abs(n2 * 3.0), math.exp(-m2)) + 1e-6)
+    assert o1 > 0 and o2 > 0 and abs(o1 - 2.0) < 1e-5 and abs(o2 - C2 / n2) < 1e-5
+    # a running maximum that starts at 0: with very negative gates the floor e^(-m) = 1 is the denominator
+    t["m.i.b"] = torch.tensor([-40.0], dtype=torch.float64)
+    tiny = P.mlstm(torch.tensor([[2.0]], dtype=torch.float64), {**t, "m.norm": torch.ones(1, dtype=torch.float64)}, "m",
+                   {"heads": 1, "dim": 1, "vdim": 1, "gate_cap": cap}, 1.0)
+    raw = math.exp(cap * math.tanh(-40.0 / cap)) * 4.0 * 2.0 / (1.0 + 1e-6)
+    assert abs(tiny[0, 0].item() - 0.5 * raw / math.sqrt(raw * raw + 1.0)) < 1e-12
+    # copies of the stream: one layer whose mixer is replaced by the identity through the maps alone
+    cfg = {"norm": {"eps": 0.0}, "streams": 2, "embedding": {"scale": 2.0}, "logit_scale": 3.0,
+           "layers": [{"type": "mlstm", "mixer": {"heads": 1, "dim": 1, "vdim": 1, "gate_cap": cap}, "mlp": None}]}
+    w = {"embed": torch.tensor([[1.0], [-1.0]], dtype=torch.float64), "final.norm": torch.zeros(1, dtype=torch.float64),
+         "head": torch.tensor([[1.0], [2.0]], dtype=torch.float64), "l0.norm1": torch.zeros(1, dtype=torch.float64),
+         "l0.hc1.in": torch.tensor([1.0, 0.5], dtype=torch.float64), "l0.hc1.out": torch.tensor([0.0, 0.0], dtype=torch.float64),
+         "l0.hc1.mix": torch.tensor([[1.0, 2.0], [3.0, 4.0]], dtype=torch.float64)}
+    w.update({"l0.mix" + k[1:]: v for k, v in t.items()})
+    seen = []
+    logits = P.forward(cfg, w, [0, 1], seen)
+    # x_1 = x_2 = +-2; the write adds nothing (out = 0): x_1' = 1 x_1 + 3 x_2 = 4 x, x_2' = 2 x_1 + 4 x_2 = 6 x; sum 10 x = +-20
+    assert torch.allclose(seen[0], torch.tensor([[20.0], [-20.0]], dtype=torch.float64))
+    assert torch.allclose(logits, torch.tensor([[3.0, 6.0], [-3.0, -6.0]], dtype=torch.float64))
+
+
+# ---------------------------------------------------------------------------
+# kernels against their statements
+# ---------------------------------------------------------------------------
+
+def _close(got, want, dtype, what, f32=2e-5, bf16=2e-2):
+    tol = f32 if dtype == torch.float32 else bf16
+    err = (got.cpu().double() - want.double()).abs().max().item()
+    assert math.isfinite(err) and err <= tol * max(1.0, want.double().abs().max().item()), (what, err)
+
+
+def _paged(lens, G, d, dv, dtype, seed, spare=3):
+    from janis_b200.kernels.ops import PAGE
+    g = torch.Generator().manual_seed(seed)
+    per = [(n + PAGE - 1) // PAGE for n in lens]
+    n_pages = sum(per) + spare
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(len(lens) + 2, max(per) + 1, dtype=torch.int32)
+    slots = torch.randperm(len(lens) + 2, generator=g)[:len(lens)].to(torch.int32)
+    at = 0
+    for s in range(len(lens)):
+        for j in range(per[s]):
+            table[int(slots[s]), j] = order[at]
+            at += 1
+    k = torch.randn(n_pages, G, PAGE, d, generator=g).to(dtype)
+    v = torch.randn(n_pages, G, PAGE, dv, generator=g).to(dtype)
+    return k, v, table, slots
+
+
+def _tables(lens, starts, slots):
+    tok_pos, tok_seq, first = [], [], []
+    for s, (n, st) in enumerate(zip(lens, starts)):
+        first.append(len(tok_pos))
+        tok_pos += list(range(st, st + n))
+        tok_seq += [s] * n
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    return (i32(tok_pos), i32(tok_seq), i32(slots), i32(first), i32(starts), i32([a + b for a, b in zip(starts, lens)]))
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,window,keep", [(4, 1, 16, 24, 3), (8, 2, 64, 128, 8), (5, 5, 10, 5, 1), (3, 1, 6, 1, 2),
+                                               (16, 16, 16, 64, 1), (6, 2, 48, 70, 4), (2, 1, 32, 130, 70)])
+def test_window_with_kept_first_positions_against_its_statement(dtype, H, G, d, window, keep):
+    """On the tensor cores (rows together; a row a CTA; a row's keys over 3 and 7 CTAs) and in the plain kernel.  Queries
+    stand at the window's edges, at page borders and far into sequences over scattered pages; under head 0 the oldest key
+    inside the window, the newest outside it, the last kept position and the first that is not kept get a large score:
+    two of them must count and two must not."""
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    lens = [1, 70, 129, 300]
+    kp, vp, table, slots = _paged(lens, G, d, d, dtype, 3)
+    pos, seq = [], []
+    for s, n in enumerate(lens):
+        for p in sorted({0, n - 1, n // 2, min(n - 1, 63), min(n - 1, 64), min(n - 1, window - 1), min(n - 1, window),
+                         min(n - 1, window + keep - 1), min(n - 1, window + keep), min(n - 1, window + keep + 1), min(n - 1, 2 * window)}):
+            pos.append(p)
+            seq.append(s)
+    T = len(pos)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(T, H * d + 3, generator=g).to(dtype)
+    hot = torch.zeros(d)
+    hot[0] = 6.0
+    q[:, :d] = (q[:, :d].float() * 0.2 + hot).to(dtype)
+    mark = {}
+    for t in range(T):
+        for j in (pos[t] - window + 1, pos[t] - window, keep - 1, keep):
+            if 0 <= j <= pos[t]:
+                mark[(seq[t], j)] = True
+    for (s, j) in mark:
+        kp[int(table[int(slots[s]), j // ops.PAGE]), 0, j % ops.PAGE] = hot.to(dtype)
+    tok_pos, tok_seq = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
+    want = torch.zeros(T, H * d, dtype=dtype)
+    R.talk_attention(q, tok_pos, tok_seq, slots, kp, vp, table, None, None, want, H, G, d, d, 0.4, 0, False, window=window,
+                     keep_first=keep)
+    blind = torch.zeros(T, H * d, dtype=dtype)
+    R.talk_attention(q, tok_pos, tok_seq, slots, kp, vp, table, None, None, blind, H, G, d, d, 0.4, 0, False, window=window)
+    assert (want.float() - blind.float()).abs().max().item() > 0.05       # leaving the kept positions out would show
+    dev = lambda x: x.cuda() if x is not None else None
+    for which, one_row, chunks in ((1, False, 1), (1, True, 1), (1, True, 3), (1, True, 7), (0, False, 1)):
+        ops.talk_attention_set_kernel(which)
+        try:
+            got = torch.full((T, H * d), float("nan"), dtype=dtype, device="cuda")
+            n = ops.talk_attention_scratch_floats(T, chunks, H, d)
+            scratch = torch.full((n,), float("nan"), device="cuda") if n else None
+            ops.talk_attention(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), None, None, got, H, G,
+                               d, d, 0.4, 0, False, one_row=one_row, max_keys=min(window + keep, 300), n_chunks=chunks,
+                               scratch=scratch, window=window, keep_first=keep)
+        finally:
+            ops.talk_attention_set_kernel(1)
+        _close(got, want, dtype, (which, one_row, chunks))
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,rot,halves,unit", [(4, 1, 16, 8, False, True), (8, 2, 64, 32, False, True), (5, 5, 10, 4, False, True),
+                                                   (3, 1, 6, 0, False, True), (2, 1, 32, 32, True, False), (6, 3, 48, 48, False, True),
+                                                   (2, 2, 24, 12, True, True)])
+def test_turn_norm_store_kernel_against_its_statement(dtype, H, G, d, rot, halves, unit):
+    """Sequences that start, that go on across a page's border, one token, and a padding sequence; the queries and both
+    pools are compared (the values are the keys as they were projected)."""
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(5)
+    lens, starts, slots = [7, 1, 70, 3, 2], [0, 63, 60, 5, 0], [2, 0, 4, 1, -1]
+    tok_pos, tok_seq, seq_slot, *_ = _tables(lens, starts, slots)
+    T = sum(lens)
+    per_seq = max(-(-(a + n) // ops.PAGE) for a, n in zip(starts, lens))
+    n_pages = 5 * per_seq
+    table = torch.randperm(n_pages, generator=g)[:5 * per_seq].view(5, per_seq).to(torch.int32)
+    rows = torch.randn(T, (H + G) * d + 5, generator=g).to(dtype)
+    inv = torch.tensor([100.0 ** (-2.0 * i / max(rot, 2)) for i in range(max(rot // 2, 1))], dtype=torch.float32)
+    kp = torch.randn(n_pages, G, ops.PAGE, d, generator=g).to(dtype)
+    vp = torch.randn(n_pages, G, ops.PAGE, d, generator=g).to(dtype)
+    want_rows, want_k, want_v = rows.clone(), kp.clone(), vp.clone()
+    R.qk_rotate_norm_store(want_rows, tok_pos, tok_seq, seq_slot, inv, rot, halves, unit, 1e-5, H, G, d, want_k, want_v, table)
+    got_rows, got_k, got_v = rows.cuda(), kp.cuda(), vp.cuda()
+    ops.qk_rotate_norm_store(got_rows, tok_pos.cuda(), tok_seq.cuda(), seq_slot.cuda(), inv.cuda(), rot, halves, unit, 1e-5, H, G, d,
+                             got_k, got_v, table.cuda())
+    _close(got_rows[:, :H * d], want_rows[:, :H * d], dtype, "queries")
+    assert torch.equal(got_rows[:, H * d:].cpu(), rows[:, H * d:])
+    _close(got_k, want_k, dtype, "keys")
+    assert torch.equal(got_v.cpu(), want_v)
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d,dr,R", [(4, 16, 8, 24), (3, 12, 6, 10), (8, 32, 32, 96), (1, 6, 2, 7), (2, 0, 4, 12)])
+def test_compressed_row_kernel_turns_halves_and_takes_queries_of_their_own(dtype, H, d, dr, R):
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as Rf
+    g = torch.Generator().manual_seed(2)
+    lens, starts, slots = [5, 1, 66, 2], [0, 63, 62, 0], [1, 3, 0, -1]
+    tok_pos, tok_seq, seq_slot, *_ = _tables(lens, starts, slots)
+    T = sum(lens)
+    per_seq = 3
+    table = torch.randperm(4 * per_seq, generator=g).view(4, per_seq).to(torch.int32)
+    rows = torch.randn(T, R + dr + 3, generator=g).to(dtype)
+    q_rows = torch.randn(T, H * (d + dr) + 2, generator=g).to(dtype)
+    wc = (1.0 + 0.1 * torch.randn(R, generator=g)).float()
+    inv = torch.tensor([100.0 ** (-2.0 * i / dr) for i in range(dr // 2)], dtype=torch.float32)
+    kp = torch.randn(4 * per_seq, 1, ops.PAGE, R + dr, generator=g).to(dtype)
+    qfull = torch.randn(T, H * (R + dr), generator=g).to(dtype)
+    want_k, want_q = kp.clone(), qfull.clone()
+    Rf.latent_rotate_store(rows, 0, H, d, dr, R, wc, 1e-5, inv, 1.0, tok_pos, tok_seq, seq_slot, want_q, want_k, table, rot=dr,
+                           q_rows=q_rows, halves=True)
+    got_k, got_q = kp.cuda(), qfull.cuda()
+    ops.latent_rotate_store(rows.cuda(), 0, H, d, dr, R, wc.cuda(), 1e-5, inv.cuda(), 1.0, tok_pos.cuda(), tok_seq.cuda(),
+                            seq_slot.cuda(), got_q, got_k, table.cuda(), rot=dr, q_rows=q_rows.cuda(), halves=True)
+    _close(got_q, want_q, dtype, "queries")
+    _close(got_k, want_k, dtype, "keys")
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d,dv", [(2, 16, 24), (3, 32, 16), (4, 64, 64), (5, 10, 6), (1, 48, 64), (2, 128, 40), (2, 200, 8)])
+def test_matrix_memory_kernel_against_its_statement(dtype, H, d, dv):
+    """A prompt step (sequences of 1 to 70 tokens, one without a slot), then a step in which some go on with several tokens
+    and some with one: outputs and the three parts of the state are compared; slots that no sequence holds stay as they were."""
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(11)
+    n_slots, groups = 6, (dv + 7) // 8
+    width = 2 * H * d + 2 * H * dv + 3
+    q_off, k_off, v_off = 3, 3 + H * d, 3 + 2 * H * d
+    st = [torch.randn(n_slots, H, dv, d, generator=g), torch.randn(n_slots, H, 1, d, generator=g).expand(n_slots, H, groups, d).contiguous(),
+          torch.randn(n_slots, H, generator=g)]
+    want_st = [x.clone() for x in st]
+    got_st = [x.cuda() for x in st]
+    bias = torch.cat([2.0 * torch.randn(H, generator=g), torch.linspace(-1.0, 5.0, H)]).float()
+    for step, (lens, starts, slots) in enumerate((([7, 1, 70, 33], [0, 0, 0, 0], [2, 0, 4, -1]), ([1, 5, 1, 17], [7, 1, 70, 0], [2, 0, 4, -1]))):
+        _, _, seq_slot, first, sstart, send = _tables(lens, starts, slots)
+        T = sum(lens)
+        if step == 0:
+            for s in slots:
+                if s >= 0:
+                    for x in want_st:
+                        x[s] = 0
+                    for x in got_st:
+                        x[s] = 0
+        rows = (torch.randn(T, width, generator=g) * 0.7).to(dtype)
+        z = (4.0 * torch.randn(T, 2 * H, generator=g)).float()
+        want = torch.zeros(T, H * dv)
+        R.mlstm_scan(rows, q_off, k_off, v_off, z, bias, 6.0, seq_slot, first, sstart, send, *want_st, want, len(lens), H, d, dv,
+                     d ** -0.5, torch.zeros(T, H, 3))
+        got = torch.full((T, H * dv), float("nan"), device="cuda")
+        ops.mlstm_scan(rows.cuda(), q_off, k_off, v_off, z.cuda(), bias.cuda(), 6.0, seq_slot.cuda(), first.cuda(), sstart.cuda(),
+                       send.cuda(), *got_st, got, len(lens), H, d, dv, d ** -0.5, torch.full((T, H, 3), float("nan"), device="cuda"))
+        _close(got, want, torch.float32, ("outputs", step), f32=2e-4)
+        for a, b, what in zip(got_st, want_st, ("memory", "normaliser", "maximum")):
+            _close(a, b, torch.float32, (what, step), f32=2e-4)
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("S,W", [(2, 64), (3, 96), (1, 72), (4, 36), (8, 1024), (2, 2304)])
+def test_stream_copies_kernels_against_their_statements(dtype, S, W):
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(4)
+    T = 37
+    x = torch.randn(T, W, generator=g)
+    h = torch.zeros(T, S * W)
+    R.hc_spread(x, h, S)
+    got_h = torch.full((T, S * W), float("nan"), device="cuda")
+    ops.hc_spread(x.cuda(), got_h, S)
+    assert torch.equal(got_h.cpu(), h)
+    h = torch.randn(T, S * W, generator=g)
+    a, b, M = torch.randn(S, generator=g), torch.randn(S, generator=g), torch.randn(S, S, generator=g)
+    w = 1.0 + 0.1 * torch.randn(W, generator=g)
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    for av, rr in ((a, None), (None, rows)):
+        n = T if rr is None else rr.numel()
+        want = torch.zeros(n, W, dtype=dtype)
+        R.hc_read_norm(h, S, av, w, 1e-5, want, rr)
+        got = torch.full((n, W), float("nan"), dtype=dtype, device="cuda")
+        ops.hc_read_norm(h.cuda(), S, av.cuda() if av is not None else None, w.cuda(), 1e-5, got, rr.cuda() if rr is not None else None)
+        _close(got, want, dtype, ("read", rr is None))
+    res = torch.randn(T, W, generator=g).to(dtype)
+    for fused in (False, True):
+        want_h, got_h = h.clone(), h.cuda()
+        want = torch.zeros(T, W, dtype=dtype)
+        got = torch.full((T, W), float("nan"), dtype=dtype, device="cuda")
+        if fused:
+            R.hc_update(want_h, res, S, M, b, a, w, 1e-5, want)
+            ops.hc_update(got_h, res.cuda(), S, M.cuda(), b.cuda(), a.cuda(), w.cuda(), 1e-5, got)
+            _close(got, want, dtype, "write and read")
+        else:
+            R.hc_update(want_h, res, S, M, b)
+            ops.hc_update(got_h, res.cuda(), S, M.cuda(), b.cuda())
+        _close(got_h, want_h, torch.float32, ("write", fused))
+
+
+@GPU
+@pytest.mark.parametrize("E,I,top,shared,soft", [(6, 2, 3, True, True), (4, 0, 1, False, True), (1, 3, 2, True, True), (16, 4, 3, True, True),
+                                                 (40, 9, 6, False, True), (8, 0, 2, True, False)])
+def test_router_with_identity_entries_and_plain_experts_against_their_statements(E, I, top, shared, soft):
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(6)
+    T, ff, sff = 53, 16, 24 if shared else 0
+    z = 3.0 * torch.randn(T, E + I + (1 if shared else 0), generator=g)
+    corr = 0.3 * torch.randn(E + I, generator=g)
+    cols = E + (1 if shared else 0) + (1 if I else 0)
+    want = torch.zeros(T, cols)
+    R.moe_route(z, corr, E, 1, 1, top, 1.0, shared, want, n_identity=I, softmax=soft)
+    got = torch.full((T, cols), float("nan"), device="cuda")
+    ops.moe_route(z.cuda(), corr.cuda(), E, 1, 1, top, 1.0, shared, got, n_identity=I, softmax=soft)
+    assert torch.equal(got.cpu() != 0, want != 0)
+    _close(got, want, torch.float32, "weights")
+    assert torch.allclose(want[:, :E].sum(1) + (want[:, -1] if I else 0), torch.ones(T), atol=1e-5)
+    for dtype in (torch.float32, torch.bfloat16):
+        gu = torch.randn(T, 2 * (E * ff + sff), generator=g).to(dtype)
+        a_want = torch.zeros(T, E * ff + sff, dtype=dtype)
+        R.moe_expert_act(gu, want, E, ff, float("inf"), sff, float("inf"), 1.0, a_want, up_add=0.0)
+        a_got = torch.full((T, E * ff + sff), float("nan"), dtype=dtype, device="cuda")
+        ops.moe_expert_act(gu.cuda(), got, E, ff, float("inf"), sff, float("inf"), 1.0, a_got, up_add=0.0)
+        _close(a_got, a_want, dtype, "activation")
+        if I:
+            out, y = torch.randn(T, 40, generator=g).to(dtype), torch.randn(T, 40, generator=g).to(dtype)
+            o_want, o_got = out.clone(), out.cuda()
+            R.moe_identity_add(o_want, y, want, cols - 1)
+            ops.moe_identity_add(o_got, y.cuda(), got, cols - 1)
+            _close(o_got, o_want, dtype, "identity")
+
+
+@GPU
+def test_head_norm_with_a_weight_per_head_and_a_logistic_gate_and_the_constant_on_logits():
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(8)
+    T, H, dv = 19, 3, 24
+    o = torch.randn(T, H * dv, generator=g)
+    w = 1.0 + 0.2 * torch.randn(H * dv, generator=g)
+    for dtype in (torch.float32, torch.bfloat16):
+        rows = torch.randn(T, H * dv + 5, generator=g).to(dtype)
+        want = torch.zeros(T, H * dv, dtype=dtype)
+        R.head_norm_gate(o, rows, 5, w, 1e-5, want, H, dv, gate="sigmoid")
+        got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
+        ops.head_norm_gate(o.cuda(), rows.cuda(), 5, w.cuda(), 1e-5, got, H, dv, gate="sigmoid")
+        _close(got, want, dtype, "head norm")
+    x = torch.randn(7, 33, generator=g)
+    assert torch.equal(ops.scale_values(x.cuda(), 2.5).cpu(), x * 2.5)
+
+
+# ---------------------------------------------------------------------------
+# the engine against the plain model
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_whole_prompts_and_first_tokens(engines, plain, on, dtype):
+    for key in keys_for(on):
+        eng, steep = engines(key, dtype, on, max_tokens=2048)
+        lens = [1, 2, 3, 70, 150] if on == "cuda" else [1, 2, 40]
+        reqs = _requests(DEK[key]["vocab"], lens, 11)
+        got = run_requests(eng, reqs, lens)
+        for r, g_ in zip(reqs, got):
+            assert_logits(g_, plain(key, steep, r), dtype, f"{key} whole {len(r)}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_prompts_of_unequal_lengths_then_decoded_together_past_every_window(engines, plain, on, dtype):
+    """Batches one after another, so that slots, pages and states are used again; a request of one token beside long ones; decoding
+    carries every window over tokens that were decoded, and the matrix memory over its stored state."""
+    for key in keys_for(on):
+        eng, steep = engines(key, dtype, on, max_tokens=2048)
+        if on == "cuda":
+            lens, prompts = [260, 1, 140, 67, 200, 30], [120, 1, 60, 64, 63, 5]
+        else:
+            lens, prompts = [40, 1, 30, 12], [20, 1, 6, 9]
+        reqs = _requests(DEK[key]["vocab"], lens, 23)
+        got = run_requests(eng, reqs, prompts, max_live=3 if on == "cuda" else 2)
+        for r, g_ in zip(reqs, got):
+            assert_logits(g_, plain(key, steep, r), dtype, f"{key} batch {len(r)}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_a_request_alone_and_in_company_and_token_by_token(engines, plain, on, dtype):
+    for key in keys_for(on)[:4]:
+        eng, steep = engines(key, dtype, on, max_tokens=2048)
+        n = 90 if on == "cuda" else 25
+        reqs = _requests(DEK[key]["vocab"], [n, 17, n // 2], 31)
+        alone = run_requests(eng, reqs[:1], [n // 3])[0]
+        together = run_requests(eng, reqs, [n // 3, 9, 4])[0]
+        one_by_one = run_requests(eng, reqs[:1], [1])[0]
+        want = plain(key, steep, reqs[0])
+        for g_, what in ((alone, "alone"), (together, "in company"), (one_by_one, "token by token")):
+            assert_logits(g_, want, dtype, f"{key} {what}")
+        if dtype == "float32" and on == "cuda":
+            assert (alone - together).abs().max().item() <= 1e-4 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+@pytest.mark.parametrize("chunk", [2, 3, 16, 64, 65])
+def test_prompts_in_pieces(engines, plain, on, dtype, chunk):
+    if on == "refs" and chunk > 16:
+        pytest.skip("long pieces run on the GPU")
+    for key in keys_for(on)[:4]:
+        eng, steep = engines(key, dtype, on, max_tokens=2048)
+        lens = [150, 66, 7] if on == "cuda" else [21, 9]
+        reqs = _requests(DEK[key]["vocab"], lens, 41)
+        got = run_in_pieces(eng, reqs, chunk)
+        for r, g_ in zip(reqs, got):
+            assert_logits(g_, plain(key, steep, r), dtype, f"{key} pieces of {chunk}, {len(r)} tokens")
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_recorded_steps(engines, plain, dtype):
+    for key in ("A", "C"):
+        eng, steep = engines(key, dtype, "cuda", max_tokens=2048)
+        reqs = _requests(DEK[key]["vocab"], [330, 300], 51)
+        got = run_requests(eng, reqs, [10, 3])
+        for r, g_ in zip(reqs, got):
+            assert_logits(g_, plain(key, steep, r), dtype, f"{key} long decoding")
+
+
+def _differ(eng, a, b, prompt_len):
+    return (run_requests(eng, [a], [prompt_len])[0][-1] - run_requests(eng, [b], [prompt_len])[0][-1]).abs().max().item()
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_token_just_inside_or_outside_the_window_and_among_the_kept_first(dek_dirs, tmp_path_factory, dtype):
+    """One layer of window attention alone: two requests that differ in one token.  The last logits must differ when the
+    token is the oldest inside the window or the last kept position, and must not when it is the newest outside the window
+    or the first position that is not kept; in the prompt's step and decoded alone."""
+    window, keep = 40, 3
+    raw = _model(120, 64, 2, 1e-6, 4.0, 1.0, [("attention", _att(4, 2, 16, 0.25, rot=8, window=window, keep=keep), None)])
+    d = str(tmp_path_factory.mktemp("dekutar_window"))
+    write_dekutar(d, raw, 77)
+    eng = make_engine(d, dtype, "cuda", max_tokens=1024)
+    try:
+        n = 150
+        base = random_tokens(120, n, 5)
+        for at, seen in ((n - window, True), (n - window - 1, False), (keep - 1, True), (keep, False), (0, True)):
+            other = list(base)
+            other[at] = (other[at] + 1) % 120
+            for prompt_len in (n, n - 20):
+                diff = _differ(eng, base, other, prompt_len)
+                assert (diff > 1e-3) == seen, (at, prompt_len, diff)
+    finally:
+        eng.close()
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_first_token_far_back_reaches_the_end_through_attention_and_memory(tmp_path_factory, dtype):
+    for kind, mixer in (("latent_attention", _lat(2, 16, 8, 16, 24, 16, 0.25)), ("mlstm", _mem(2, 16, 16, 10.0))):
+        raw = _model(120, 64, 2, 1e-6, 4.0, 1.0, [(kind, mixer, None)])
+        d = str(tmp_path_factory.mktemp("dekutar_far"))
+        write_dekutar(d, raw, 78)
+        eng = make_engine(d, dtype, "cuda", max_tokens=1024)
+        try:
+            base = random_tokens(120, 260, 6)
+            other = [(base[0] + 1) % 120] + base[1:]
+            for prompt_len in (260, 200):
+                assert _differ(eng, base, other, prompt_len) > 1e-4, (kind, prompt_len)
+        finally:
+            eng.close()
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(engines, plain, dtype):
+    from tests.plain import dekutar_plain as P  # noqa: F401
+    for key in ("A", "B"):
+        eng, steep = engines(key, dtype, "cuda", max_tokens=2048)
+        prompts = _requests(DEK[key]["vocab"], [33, 5, 70], 61)
+        replies = eng.generate(prompts, temp=0.0, max_tokens=8, stop=())
+        assert all(len(r) == 8 for r in replies)
+        for p, r in zip(prompts, replies):
+            seq = list(p)
+            for tok in r:
+                logits = plain(key, steep, seq)[-1]
+                assert logits[tok] >= logits.max() - (1e-4 if dtype == "float32" else 4e-2) * logits.abs().max(), (key, len(seq))
+                seq.append(tok)
+
+
+@GPU
+def test_trace_replay_and_command_line_as_a_user_runs_them(dek_dirs, plain, tmp_path):
+    key, steep = "A", False
+    reqs = _requests(DEK[key]["vocab"], [40, 9], 71)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": reqs[0][:30], "want": [0, 29]}, {"id": "b", "tokens": reqs[1][:5], "want": [4]}], "end": []}]
+    for i in range(10):
+        ents = [{"id": "a", "tokens": [reqs[0][30 + i]], "want": [0]}]
+        if 5 + i < 9:
+            ents.append({"id": "b", "tokens": [reqs[1][5 + i]], "want": [0]})
+        steps.append({"step": i + 1, "entries": ents, "end": ["b"] if 5 + i == 8 else (["a"] if i == 9 else [])})
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", dek_dirs[(key, steep)], "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "256"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    import numpy as np
+    V = DEK[key]["vocab"]
+    wa, wb = plain(key, steep, reqs[0]), plain(key, steep, reqs[1])
+    first = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V).copy())
+    assert_logits(first, torch.stack([wa[0], wa[29], wb[4]]), "float32", "trace step 0")
+    for i in range(10):
+        got = torch.from_numpy(np.fromfile(out / f"{i + 1}.f32", dtype="<f4").reshape(-1, V).copy())
+        want = [wa[30 + i]] + ([wb[5 + i]] if 5 + i < 9 else [])
+        assert_logits(got, torch.stack(want), "float32", f"trace step {i + 1}")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "janis"), "generate", "--model", dek_dirs[(key, steep)], "--dtype", "float32",
+                        "--ids", ",".join(map(str, reqs[1])), "--max-tokens", "4", "--temp", "0", "--stop", ""],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    seq = list(reqs[1])
+    for _ in range(4):
+        seq.append(int(plain(key, steep, seq)[-1].argmax()))
+    assert ",".join(map(str, seq[len(reqs[1]):])) in p.stdout.replace(" ", ""), p.stdout
