@@ -546,10 +546,36 @@ def vivazen_like(gemma: dict, layers: int) -> dict:
             "postln_alpha": 2.0, "layers": out}
 
 
+def dekutar_like(gemma: dict, layers: int) -> dict:
+    """A Dekutar configuration with the layer sizes of a Gemma2 one: the same width, heads, head size, and vocabulary; two
+    copies of the stream; layers take turns as "latent_attention" (as many heads, each half the head size plain and a
+    quarter rotated, values of half the head size, a compressed row as wide as one head, queries through a row of three
+    heads' width), "attention" (Gemma2's heads and key/value heads, half the head turned, Gemma2's window with four kept
+    first positions), "mlstm" (as many heads, key channels half the head size, at most 256, values of the head size) and
+    "attention" again; every feed-forward is a mixture of 16 experts of a quarter of the dense width and 4 identity
+    entries, 4 chosen, with a shared expert of that width: as many active feed-forward weights a token as the dense layer."""
+    hd, W, ff = int(gemma["head_dim"]), int(gemma["hidden_size"]), int(gemma["intermediate_size"])
+    H, G = gemma["num_attention_heads"], gemma["num_key_value_heads"]
+    lat = {"heads": H, "dim": hd // 2, "rot_dim": hd // 4, "vdim": hd // 2, "kv_rank": hd, "q_rank": 3 * hd,
+           "scale": (hd // 2 + hd // 4) ** -0.5, "rot": {"base": 10000.0, "dims": hd // 4}}
+    att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"base": 10000.0, "dims": hd // 2},
+           "mask": {"size": int(gemma.get("sliding_window", 4096)), "keep_first": 4}}
+    mem = {"heads": H, "dim": min(256, hd // 2), "vdim": hd, "gate_cap": 15.0}
+    e_ff = max(8, ff // 4 // 8 * 8)
+    moe = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": e_ff}, "router": {"experts": 16, "identity": 4, "top": 4}}
+    kinds = (("latent_attention", lat), ("attention", att), ("mlstm", mem), ("attention", att))
+    out = [{"type": kinds[i % 4][0], "mixer": copy.deepcopy(kinds[i % 4][1]), "mlp": copy.deepcopy(moe)} for i in range(layers)]
+    return {"architecture": "Dekutar", "vocab": gemma["vocab_size"], "width": W, "streams": 2, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": out}
+
+
 _TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_norm_gate", "bias_act", "add_rmsnorm", "rmsnorm"),
           "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act"),
           "nosolix": ("talk_attention", "qkv_rotate_store", "selective_scan", "causal_conv_silu", "gate_group_norm",
                       "moe_route", "moe_expert_act", "dyt_norm", "rmsnorm_accumulate", "sigmoid_gate", "bias_act"),
+          "dekutar": ("talk_attention", "talk_attention_rows", "qk_rotate_norm_store", "latent_rotate_store", "head_linear", "mlstm_scan",
+                      "head_norm_gate", "hc_update", "hc_read_norm", "hc_spread", "sigmoid_gate", "moe_route", "moe_expert_act",
+                      "moe_identity_add", "rmsnorm"),
           "vivazen": ("talk_attention", "talk_attention_rows", "qkv_conv_norm_store", "latent_rotate_store", "head_linear", "group_norm", "round_rows",
                       "sigmoid_gate", "gated_act")}
 
@@ -609,19 +635,24 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
                     seen = min(seen, (context - 1) % mixer.block + 1) if getattr(mixer, "block", 0) else seen
                     seen = min(seen, mixer.window) if getattr(mixer, "window", 0) else seen
                     kv_bytes += batch * seen * need.n_kv_heads * (need.head_dim + need.value_dim) * 2
-                elif isinstance(need, StateNeed) and name == "state":      # (a convolution's kept inputs are another kernel's)
+                elif isinstance(need, StateNeed) and name in ("state", "memory"):      # (a convolution's kept inputs are another kernel's)
                     gla_flops += mixer.prompt_flops(prefill_tokens)
+                    state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
+                elif isinstance(need, StateNeed) and name in ("normaliser", "maximum"):   # the matrix memory's other parts
                     state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
     att_name = "attn_prefill" if kind == "gemma2" else "talk_attention"
     dec_name = "attn_decode" if kind == "gemma2" else "talk_attention"
     if kernels["decode_us"].get("talk_attention_rows"):      # decode steps through the kernels that take single rows
         dec_name = "talk_attention_rows"
-    scan_name = "selective_scan" if kind == "nosolix" else "gla_scan"
+    scan_name = {"nosolix": "selective_scan", "dekutar": "mlstm_scan"}.get(kind, "gla_scan")
     roof = {}
     if kernels["prefill_us"].get(att_name):
         roof["attention_prefill_frac_of_bf16_peak"] = round(att_flops / (kernels["prefill_us"][att_name] * 1e-6) / (pk["bf16_tflops"] * 1e12), 5)
-    if kernels["decode_us"].get(dec_name):
-        roof["attention_decode_frac_of_copy_bandwidth"] = round(kv_bytes / (kernels["decode_us"][dec_name] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    dec_us = kernels["decode_us"].get(dec_name)
+    if kind == "dekutar":       # its two attentions decode through different kernels: both kernels' time against both lines' bytes
+        dec_us = (kernels["decode_us"].get("talk_attention") or 0.0) + (kernels["decode_us"].get("talk_attention_rows") or 0.0)
+    if dec_us:
+        roof["attention_decode_frac_of_copy_bandwidth"] = round(kv_bytes / (dec_us * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
     if kernels["prefill_us"].get(scan_name):
         roof["recurrence_prefill_tflops_fp32"] = round(gla_flops / (kernels["prefill_us"][scan_name] * 1e-6) / 1e12, 3)
     if kernels["decode_us"].get(scan_name):
@@ -635,13 +666,21 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
             roof[f"{nm}_prefill_frac_of_copy_bandwidth"] = round(n_norm * T * model.hidden * 10 / (kernels["prefill_us"][nm] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
     # the kernels between an attention's projection and its scores (rotate or filter, norm, write the cache line): the
     # projected rows read once and written once
-    for nm in ("qkv_rotate_store", "qkv_conv_norm_store"):
+    if kernels["prefill_us"].get("hc_update"):
+        # the write of a sublayer's output into the copies of the stream with the next read: every copy read and written
+        # as floats, the output read and the next input written in the activation type
+        n_norm = sum(2 if getattr(model.blocks[c.layer], "feed_forward", None) is not None else 1 for c in model.schedule)
+        copies = model.stream_width // model.hidden
+        roof["hc_update_prefill_frac_of_copy_bandwidth"] = round(n_norm * T * model.hidden * (8 * copies + 4) / (kernels["prefill_us"]["hc_update"] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    for nm in ("qkv_rotate_store", "qkv_conv_norm_store", "qk_rotate_norm_store"):
         if kernels["prefill_us"].get(nm):
             chans = 0
             for call in model.schedule:
                 for mixer in _leaf_mixers(model.blocks[call.layer].mixer):
                     if hasattr(mixer, "n_kv_heads") and any(isinstance(n, KVNeed) for n in mixer.cache_needs().values()):
                         own = bool(getattr(mixer, "own_kv", True))
+                        if (nm == "qk_rotate_norm_store") != bool(getattr(mixer, "values_from_keys", False)):
+                            continue
                         chans += mixer.n_heads * mixer.key_dim + own * mixer.n_kv_heads * (mixer.key_dim + mixer.value_dim)
             for mode, rows_n in (("prefill", T), ("decode", batch)):
                 if chans and kernels[f"{mode}_us"].get(nm):
@@ -658,7 +697,7 @@ def compare(sizes=("gemma2-2b", "gemma2-9b", "gemma2-27b"), layers: int = 4, pre
     weights: prompt tokens a second, decode tokens a second, and the device time of each design's own kernels in
     one prompt step and one decode step with what fraction of the roofline that is."""
     pk, pk_kind = peaks()
-    rec = {"compare": f"{design} beside {'sigalorn' if design in ('nosolix', 'vivazen') else 'gemma2'}", "dtype": "bf16", "data": "synthetic",
+    rec = {"compare": f"{design} beside {'sigalorn' if design in ('nosolix', 'vivazen', 'dekutar') else 'gemma2'}", "dtype": "bf16", "data": "synthetic",
            "peaks": pk_kind, "prefill_tokens": prefill_tokens, "batch": batch, "context": context, "steps": steps, "sizes": {}}
     for name in sizes:
         gemma = dict(load_config(name), num_hidden_layers=layers)
@@ -667,6 +706,11 @@ def compare(sizes=("gemma2-2b", "gemma2-9b", "gemma2-27b"), layers: int = 4, pre
             rec["sizes"][name] = {
                 "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup),
                 "vivazen": _measure_design(vivazen_like(gemma, layers), "vivazen", pk, prefill_tokens, batch, context, steps, warmup)}
+            continue
+        if design == "dekutar":      # beside the design with the like kernels: attention through the same kernel, a matrix of state per head
+            rec["sizes"][name] = {
+                "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup),
+                "dekutar": _measure_design(dekutar_like(gemma, layers), "dekutar", pk, prefill_tokens, batch, context, steps, warmup)}
             continue
         if design == "nosolix":      # beside the closest design the library has: recurrent layers between attention over a limited span
             rec["sizes"][name] = {
@@ -700,8 +744,8 @@ def main(argv=None) -> int:
                     "instead of sequences that all reach --context")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
-    ap.add_argument("--compare", choices=["sigalorn", "nosolix", "vivazen"], default="",
-                    help="instead of the benchmark: Sigalorn beside Gemma2, or Nosolix or Vivazen beside Sigalorn, at equal layer "
+    ap.add_argument("--compare", choices=["sigalorn", "nosolix", "vivazen", "dekutar"], default="",
+                    help="instead of the benchmark: Sigalorn beside Gemma2, or Nosolix, Vivazen or Dekutar beside Sigalorn, at equal layer "
                     "sizes (prompt and decode throughput, and each design's own kernels against their rooflines); "
                     "--config picks one size")
     a = ap.parse_args(argv)

@@ -227,7 +227,8 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
 // (token, head) the three factors keep = e^(f + m' - m), take = e^(i - m), floor = e^(-m); m is loaded from and
 // written back to the cache.  `mlstm_scan`: the recurrence itself in the layout of the scan above (16 lanes a column
 // of C, each holding a run of key channels), with n as one more column whose value is 1 in every CTA (so every
-// CTA owns a copy of n: the cache keeps one per group of columns and no CTA waits for another).
+// CTA owns a copy of n: the cache keeps one per group of columns and no CTA waits for another).  A tile's n . q pass
+// through shared memory and its results are divided and written while the next tile is staged.
 // ---------------------------------------------------------------------------
 template <int DUMMY>
 __global__ void __launch_bounds__(32)
@@ -276,8 +277,10 @@ mlstm_gates_kernel(const float* __restrict__ z, const float* __restrict__ bias, 
 constexpr int MLSTM_GROUPS = GLA_COLS + 2;      // the value columns, the column of n, and one idle group that fills the last warp
 constexpr int MLSTM_THREADS = MLSTM_GROUPS * GLA_KS;
 
+// (a decode step is over in a few waves of CTAs, so what an SM holds at once counts: four CTAs at the smallest key
+// size, three at the middle one)
 template <typename T, int DPT>
-__global__ void __launch_bounds__(MLSTM_THREADS)
+__global__ void __launch_bounds__(MLSTM_THREADS, DPT <= 4 ? 4 : (DPT <= 8 ? 3 : 1))
 mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__ coef,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                   const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state_c,
@@ -285,9 +288,10 @@ mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict
     constexpr int RUN = DPT + 4, TOK = GLA_KS * RUN;       // floats of a lane's run, of a token
     constexpr int TT = DPT >= 16 ? 8 : 16;                 // tokens staged per round
     __shared__ __align__(16) float q_s[TT * TOK];
-    __shared__ __align__(16) float k_s[TT * TOK];          // k times the token's `take`
+    __shared__ __align__(16) float k_s[TT * TOK];
     __shared__ float v_s[TT * GLA_COLS];
-    __shared__ float keep_s[TT], take_s[TT], floor_s[TT], nq_s[TT];
+    __shared__ float keep_s[TT], take_s[TT];
+    __shared__ float floor_s[2][TT], nq_s[2][TT];          // by the tile's parity: a tile's results leave while the next is staged
     const int d = g.d, dv = g.dv, H = g.H;
     const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS, n_groups = gridDim.z;
     const int tid = threadIdx.x, ks = tid % GLA_KS, grp = tid / GLA_KS, col = col0 + grp;
@@ -355,15 +359,25 @@ mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict
             }
         }
     };
+    constexpr int SHARE = GLA_KS / TT;                      // lanes that end up with the same token's sum: 1, or 2 with tiles of 8 tokens
+    const int my_tt = ks / SHARE;
+    const bool writer = live && !is_n && ks % SHARE == 0;
+    float held = 0.f;                                       // this lane's numerator of the tile before
+    auto write_out = [&](int t0, int par) {
+        // o = C^T q / (max(|n . q|, e^(-m)) + 1e-6), with n . q from the group that carries n
+        if (writer && t0 + my_tt < n_tok)
+            o_out[(size_t)(row0 + t0 + my_tt) * H * dv + h * dv + col] = held / (fmaxf(fabsf(nq_s[par][my_tt]), floor_s[par][my_tt]) + 1e-6f);
+    };
     fetch(0);
-    for (int t0 = 0; t0 < n_tok; t0 += TT) {
-        __syncthreads();                       // the tile before has been read
+    int par = 0;
+    for (int t0 = 0; t0 < n_tok; t0 += TT, par ^= 1) {
+        __syncthreads();                       // the tile before has been read, and its n . q stand in shared memory
+        if (t0 > 0) write_out(t0 - TT, par ^ 1);
         if (tid >= NT && tid - NT < TT) {
             keep_s[tid - NT] = cf_keep;
             take_s[tid - NT] = cf_take;
-            floor_s[tid - NT] = cf_floor;
+            floor_s[par][tid - NT] = cf_floor;
         }
-        __syncthreads();
         if (tid < NT) {
 #pragma unroll
             for (int e = 0; e < PER; ++e) {
@@ -379,7 +393,7 @@ mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict
                 }
                 const int at = tt * TOK + (c / DPT) * RUN + c % DPT;
                 q_s[at] = qv[e] * g.q_scale;
-                k_s[at] = kv[e] * take_s[tt];
+                k_s[at] = kv[e];
             }
             if (tid < TT * GLA_COLS) v_s[tid] = vv;
         }
@@ -391,7 +405,7 @@ mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict
         for (int tt = 0; tt < TT; ++tt) {
             part_o[tt] = 0.f;
             if (tt >= tt_n) continue;
-            const float v = is_n ? 1.f : (grp < GLA_COLS ? v_s[tt * GLA_COLS + grp] : 0.f);
+            const float v = (is_n ? 1.f : (grp < GLA_COLS ? v_s[tt * GLA_COLS + grp] : 0.f)) * take_s[tt];
             const float keep = keep_s[tt];
             const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
             const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
@@ -429,13 +443,11 @@ mlstm_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict
                 part_o[0] += __shfl_xor_sync(0xffffffffu, part_o[0], off);
             }
         }
-        constexpr int SHARE = GLA_KS / TT;                  // 1, or 2 with tiles of 8 tokens
-        const int tt = ks / SHARE;
-        if (is_n && ks % SHARE == 0) nq_s[tt] = part_o[0];
-        __syncthreads();
-        if (live && !is_n && ks % SHARE == 0 && t0 + tt < n_tok)
-            o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = part_o[0] / (fmaxf(fabsf(nq_s[tt]), floor_s[tt]) + 1e-6f);
+        if (is_n && ks % SHARE == 0) nq_s[par][my_tt] = part_o[0];
+        held = part_o[0];
     }
+    __syncthreads();
+    write_out((n_tok - 1) / TT * TT, par ^ 1);
     if (st != nullptr) {
 #pragma unroll
         for (int ii = 0; ii < DPT; ++ii) {
