@@ -286,6 +286,21 @@ moe_identity_add_kernel(T* __restrict__ out, const T* __restrict__ y, const floa
                         int width, size_t n) {
     grid_dependents_launch();
     grid_dependency_wait();
+    constexpr int V = Vec16<T>::N;
+    if (width % V == 0 && (((uintptr_t)out | (uintptr_t)y) & 15) == 0) {
+        // 16 bytes a thread; the pieces of a row share its weight
+        for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V; i < n; i += (size_t)gridDim.x * blockDim.x * V) {
+            const float w = wts[(i / width) * wts_stride + w_col];
+            if (w == 0.f) continue;
+            float a[V], b[V];
+            Vec16<T>::load(out + i, a);
+            Vec16<T>::load(y + i, b);
+#pragma unroll
+            for (int e = 0; e < V; ++e) a[e] = fmaf(w, b[e], a[e]);
+            Vec16<T>::store(out + i, a);
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const float w = wts[(i / width) * wts_stride + w_col];
         if (w != 0.f) out[i] = from_float<T>(fmaf(w, to_float(y[i]), to_float(out[i])));

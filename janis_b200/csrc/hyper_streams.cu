@@ -26,11 +26,29 @@ hc_spread_kernel(const float* __restrict__ x, float* __restrict__ h, int S, int 
     }
 }
 
+// four neighbouring elements at once: 16 bytes of floats, 8 of bfloat16
+__device__ __forceinline__ void load4(const float* p, float (&y)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    y[0] = v.x; y[1] = v.y; y[2] = v.z; y[3] = v.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&y)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    y[0] = __uint_as_float(v.x << 16); y[1] = __uint_as_float(v.x & 0xffff0000u);
+    y[2] = __uint_as_float(v.y << 16); y[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float (&y)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(y[0], y[1], y[2], y[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&y)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(y[0], y[1]), b = __floats2bfloat162_rn(y[2], y[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 hc_read_norm_kernel(const float* __restrict__ h, const int* __restrict__ rows, const float* __restrict__ a,
                     const float* __restrict__ w, float eps, T* __restrict__ out, int S, int W) {
-    extern __shared__ float hc_u[];
+    extern __shared__ __align__(16) float hc_u[];
     __shared__ float scratch[32];
     const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     grid_dependents_launch();
@@ -41,17 +59,47 @@ hc_read_norm_kernel(const float* __restrict__ h, const int* __restrict__ rows, c
     const size_t row = rows != nullptr ? (size_t)rows[r] : (size_t)r;
     const float* x = h + row * S * W;
     float ss = 0.f;
-    for (int c = tid; c < W; c += nt) {
-        float u = 0.f;
+    T* o = out + (size_t)r * W;
+    const bool vec = (W & 3) == 0 && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
+    if (vec) {
+        // (the sums run in the same order per element as below: a row's result does not depend on the path)
+        for (int c = tid * 4; c < W; c += nt * 4) {
+            float u[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s)
-            if (s < S) u = fmaf(av[s], x[(size_t)s * W + c], u);
-        hc_u[c] = u;
-        ss = fmaf(u, u, ss);
+            for (int s = 0; s < HC_MAX; ++s)
+                if (s < S) {
+                    float v[4];
+                    load4(x + (size_t)s * W + c, v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) u[e] = fmaf(av[s], v[e], u[e]);
+                }
+            store4(hc_u + c, u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(u[e], u[e], ss);
+        }
+    } else {
+        for (int c = tid; c < W; c += nt) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < HC_MAX; ++s)
+                if (s < S) u = fmaf(av[s], x[(size_t)s * W + c], u);
+            hc_u[c] = u;
+            ss = fmaf(u, u, ss);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)W + eps);
-    T* o = out + (size_t)r * W;
+    if (vec) {
+        for (int c = tid * 4; c < W; c += nt * 4) {
+            float u[4], wv[4];
+            load4(hc_u + c, u);
+            load4(w + c, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) u[e] = u[e] * inv * wv[e];
+            store4(o + c, u);
+        }
+        return;
+    }
     for (int c = tid; c < W; c += nt) o[c] = from_float<T>(hc_u[c] * inv * w[c]);
 }
 
@@ -60,7 +108,7 @@ __global__ void __launch_bounds__(256)
 hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* __restrict__ M, const float* __restrict__ b,
                  const float* __restrict__ a_next, const float* __restrict__ w_next, float eps_next,
                  TO* __restrict__ out, int S, int W) {
-    extern __shared__ float hc_u[];
+    extern __shared__ __align__(16) float hc_u[];
     __shared__ float scratch[32];
     __shared__ float m_s[HC_MAX * HC_MAX], b_s[HC_MAX], a_s[HC_MAX];
     const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
@@ -76,7 +124,46 @@ hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* 
     const T* rr = res + (size_t)r * W;
     const bool read = w_next != nullptr;
     float ss = 0.f;
-    for (int c = tid; c < W; c += nt) {
+    const bool vec = (W & 3) == 0 && (((uintptr_t)h | (uintptr_t)res | (uintptr_t)out | (uintptr_t)w_next) & 15) == 0;
+    for (int c = tid * 4; vec && c < W; c += nt * 4) {
+        // four elements a thread: every copy 16 bytes a load and a store; the sums per element in the order of the loop below
+        float y[4], fresh[HC_MAX][4];
+        load4(rr + c, y);
+#pragma unroll
+        for (int k = 0; k < HC_MAX; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) fresh[k][e] = 0.f;
+#pragma unroll
+        for (int s = 0; s < HC_MAX; ++s)
+            if (s < S) {
+                float old[4];
+                load4(x + (size_t)s * W + c, old);
+#pragma unroll
+                for (int k = 0; k < HC_MAX; ++k)
+                    if (k < S) {
+                        const float m = m_s[s * S + k];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) fresh[k][e] = fmaf(m, old[e], fresh[k][e]);
+                    }
+            }
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < HC_MAX; ++k)
+            if (k < S) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    fresh[k][e] = fmaf(b_s[k], y[e], fresh[k][e]);
+                    u[e] = fmaf(a_s[k], fresh[k][e], u[e]);
+                }
+                store4(x + (size_t)k * W + c, fresh[k]);
+            }
+        if (read) {
+            store4(hc_u + c, u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(u[e], u[e], ss);
+        }
+    }
+    for (int c = tid; !vec && c < W; c += nt) {
         float old[HC_MAX];
 #pragma unroll
         for (int s = 0; s < HC_MAX; ++s) old[s] = s < S ? x[(size_t)s * W + c] : 0.f;
@@ -102,6 +189,17 @@ hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* 
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)W + eps_next);
     TO* o = out + (size_t)r * W;
+    if (vec) {
+        for (int c = tid * 4; c < W; c += nt * 4) {
+            float u[4], wv[4];
+            load4(hc_u + c, u);
+            load4(w_next + c, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) u[e] = u[e] * inv * wv[e];
+            store4(o + c, u);
+        }
+        return;
+    }
     for (int c = tid; c < W; c += nt) o[c] = from_float<TO>(hc_u[c] * inv * w_next[c]);
 }
 
