@@ -1284,7 +1284,7 @@ def latent_rotate_store(rows, lat_off: int, H: int, d: int, dr: int, R: int, wc,
         rows.data_ptr(), _DT[rows.dtype], width, int(lat_off),
         _t(q_rows, "q_rows", rows.dtype, (T, None)) if q_rows is not None else None,
         q_rows.shape[1] if q_rows is not None else 0, 1 if halves else 0, T, H, d, dr, dr if rot is None else int(rot), R,
-        _t(wc, "wc", torch.float32, (R,)), float(eps), _t(inv_freq, "inv_freq", torch.float32, (dr // 2,)), float(amp),
+        _t(wc, "wc", torch.float32, (R,)), float(eps), _t(inv_freq, "inv_freq", torch.float32, (max(dr // 2, 1),) if dr < 2 else (dr // 2,)), float(amp),
         _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32),
         _t(qfull, "qfull", rows.dtype, (T, H * (R + dr))), kpool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         _stream()))
