@@ -552,7 +552,7 @@ def dekutar_like(gemma: dict, layers: int) -> dict:
     quarter rotated, values of half the head size, a compressed row as wide as one head, queries through a row of three
     heads' width), "attention" (Gemma2's heads and key/value heads, half the head turned, Gemma2's window with four kept
     first positions), "mlstm" (as many heads, key channels half the head size, at most 256, values of the head size) and
-    "attention" again; every feed-forward is a mixture of 16 experts of a quarter of the dense width and 4 identity
+    "attention" again; every feed-forward is a mixture of 16 experts of a quarter of the dense width and 2 identity
     entries, 4 chosen, with a shared expert of that width: as many active feed-forward weights a token as the dense layer."""
     hd, W, ff = int(gemma["head_dim"]), int(gemma["hidden_size"]), int(gemma["intermediate_size"])
     H, G = gemma["num_attention_heads"], gemma["num_key_value_heads"]
@@ -560,9 +560,9 @@ def dekutar_like(gemma: dict, layers: int) -> dict:
            "scale": (hd // 2 + hd // 4) ** -0.5, "rot": {"base": 10000.0, "dims": hd // 4}}
     att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"base": 10000.0, "dims": hd // 2},
            "mask": {"size": int(gemma.get("sliding_window", 4096)), "keep_first": 4}}
-    mem = {"heads": H, "dim": min(256, hd // 2), "vdim": hd, "gate_cap": 15.0}
+    mem = {"heads": H, "dim": min(256, hd // 2), "vdim": hd, "gate_cap": 10.0}
     e_ff = max(8, ff // 4 // 8 * 8)
-    moe = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": e_ff}, "router": {"experts": 16, "identity": 4, "top": 4}}
+    moe = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": e_ff}, "router": {"experts": 16, "identity": 2, "top": 4}}
     kinds = (("latent_attention", lat), ("attention", att), ("mlstm", mem), ("attention", att))
     out = [{"type": kinds[i % 4][0], "mixer": copy.deepcopy(kinds[i % 4][1]), "mlp": copy.deepcopy(moe)} for i in range(layers)]
     return {"architecture": "Dekutar", "vocab": gemma["vocab_size"], "width": W, "streams": 2, "embedding": {"scale": 1.0},

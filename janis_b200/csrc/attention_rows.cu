@@ -28,6 +28,7 @@ struct RowsShape {
     int H, G, d, dv;
     int v_stride;       // elements between the values of neighbouring positions (dv, or d when the values lie in the keys)
     int window;         // keys are seen among the row's last `window` positions (0: all earlier ones)
+    int keep_first;     // with a window: the sequence's first `keep_first` positions stay seen behind it
     int chunk;          // keys a CTA takes
     int n_chunks;       // CTAs a row
     int sink;           // 0 none; 1 a key of score 0 without a value; 2 learnt values
@@ -52,11 +53,18 @@ template <> __device__ __forceinline__ void rows_unpack<bf16>(const uint4& raw, 
     }
 }
 
-__device__ __forceinline__ void rows_range(const RowsShape& sh, int pos, int c, int& j0, int& j1) {
-    const int first = sh.window > 0 ? max(0, pos - sh.window + 1) : 0;
-    j0 = first + c * sh.chunk;
-    j1 = min(pos, j0 + sh.chunk - 1);
+// The keys a row sees are counted through: the kept first positions that lie before the window, then first .. pos.
+// A chunk takes the counts j0 .. j1; rows_key gives a count's position in the sequence.
+struct RowsKeys { int first, kept; };
+__device__ __forceinline__ RowsKeys rows_range(const RowsShape& sh, int pos, int c, int& j0, int& j1) {
+    RowsKeys k;
+    k.first = sh.window > 0 ? max(0, pos - sh.window + 1) : 0;
+    k.kept = sh.window > 0 ? min(sh.keep_first, k.first) : 0;
+    j0 = c * sh.chunk;
+    j1 = min(k.kept + pos - k.first, j0 + sh.chunk - 1);
+    return k;
 }
+__device__ __forceinline__ int rows_key(const RowsKeys& k, int n) { return n < k.kept ? n : k.first + n - k.kept; }
 
 // scores [T, H, n_chunks * chunk], part [T, n_chunks, H, 2]
 template <typename T>
@@ -75,7 +83,7 @@ rows_scores_kernel(const T* __restrict__ q_rows, int q_row_elems, const int* __r
     grid_dependents_launch();
     const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
     int j0, j1;
-    rows_range(sh, pos, c, j0, j1);
+    const RowsKeys keys = rows_range(sh, pos, c, j0, j1);
     grid_dependency_wait();
     float* prt = part + ((size_t)t * sh.n_chunks + c) * H * 2;
     if (slot < 0 || j0 > j1) {
@@ -88,7 +96,7 @@ rows_scores_kernel(const T* __restrict__ q_rows, int q_row_elems, const int* __r
     {
         const int* table = page_table + (size_t)slot * table_stride;
         for (int jj = tid; jj < n_keys; jj += ROWS_THREADS) {
-            const int j = j0 + jj;
+            const int j = rows_key(keys, j0 + jj);
             base_s[jj] = table[j / JANIS_PAGE] * G * JANIS_PAGE + j % JANIS_PAGE;
         }
     }
@@ -203,13 +211,13 @@ rows_values_kernel(const float* __restrict__ scores, const float* __restrict__ f
     grid_dependents_launch();
     const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
     int j0, j1;
-    rows_range(sh, pos, c, j0, j1);
+    const RowsKeys keys = rows_range(sh, pos, c, j0, j1);
     grid_dependency_wait();
     if (slot < 0 || j0 > j1) return;                // (the sum leaves such chunks out)
     const int n_keys = j1 - j0 + 1;
     const int* table = page_table + (size_t)slot * table_stride;
     for (int jj = tid; jj < n_keys; jj += ROWS_THREADS) {
-        const int j = j0 + jj;
+        const int j = rows_key(keys, j0 + jj);
         base_s[jj] = table[j / JANIS_PAGE] * G * JANIS_PAGE + j % JANIS_PAGE;
     }
     const size_t row_len = (size_t)sh.n_chunks * chunk;
@@ -301,8 +309,8 @@ rows_sum_kernel(const float* __restrict__ o_part, const int* __restrict__ tok_po
     const int t = blockIdx.y, n = sh.H * sh.dv, i = (blockIdx.x * ROWS_THREADS + threadIdx.x) * 4;
     grid_dependents_launch();
     const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
-    const int first = sh.window > 0 ? max(0, pos - sh.window + 1) : 0;
-    const int n_valid = slot < 0 ? 0 : min(sh.n_chunks, (pos - first) / sh.chunk + 1);
+    const int first = sh.window > 0 ? max(0, pos - sh.window + 1) : 0, kept = sh.window > 0 ? min(sh.keep_first, first) : 0;
+    const int n_valid = slot < 0 ? 0 : min(sh.n_chunks, (kept + pos - first) / sh.chunk + 1);
     grid_dependency_wait();
     if (i >= n) return;
     const float* src = o_part + (size_t)t * sh.n_chunks * n + i;
@@ -372,8 +380,9 @@ JANIS_EXPORT int janis_talk_attention_rows(const void* q_rows, int dtype, int q_
                                            const int* page_table, int table_stride, const float* talk, void* out, int T,
                                            int H, int G, int d, int dv, float scale, int sink, int max_keys, int window,
                                            float cap, const float* sink_values, int values_in_keys, float* scratch,
-                                           long long scratch_floats, cudaStream_t stream) {
+                                           long long scratch_floats, int keep_first, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return fail("talk_attention_rows: %d kept first positions need a window", keep_first);
     const long long want = janis_talk_attention_rows_floats(dtype, T, H, G, d, dv, max_keys);
     if (want <= 0) return fail("talk_attention_rows: sizes not taken (%d heads over %d, %d and %d features)", H, G, d, dv);
     if (scratch == nullptr || scratch_floats < want) return fail("talk_attention_rows: scratch of %lld floats, %lld wanted", scratch_floats, want);
@@ -387,6 +396,7 @@ JANIS_EXPORT int janis_talk_attention_rows(const void* q_rows, int dtype, int q_
     sh.H = H; sh.G = G; sh.d = d; sh.dv = dv;
     sh.v_stride = values_in_keys ? d : dv;
     sh.window = window;
+    sh.keep_first = keep_first;
     sh.sink = sink ? (sink_values != nullptr ? 2 : 1) : 0;
     sh.scale = scale;
     sh.cap = cap;

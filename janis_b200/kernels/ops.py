@@ -144,7 +144,7 @@ def mixers():
         lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_talk_attention_rows_floats.argtypes = [I, I, I, I, I, I, I]
         lib.janis_talk_attention_rows_floats.restype = c_longlong
-        lib.janis_talk_attention_rows.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, F, P, I, P, c_longlong, P]
+        lib.janis_talk_attention_rows.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, F, P, I, P, c_longlong, I, P]
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, I, I, P]
         lib.janis_mlstm_scan.argtypes = [P, I, I, I, I, I, P, P, F, P, I, P, P, P, P, P, P, P, P, I, I, I, I, F, P]
@@ -884,13 +884,14 @@ def talk_attention_rows_floats(dtype, T: int, H: int, G: int, d: int, dv: int, m
 
 def talk_attention_rows(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, out, H: int, G: int, d: int,
                         dv: int, scale: float, scratch, max_keys: int, sink: bool = False, window: int = 0, cap: float = 0.0,
-                        sink_values=None, values_in_keys: bool = False):
+                        sink_values=None, values_in_keys: bool = False, keep_first: int = 0):
     """`talk_attention` for a decode step (every row a query position of a sequence of its own): keys and values are
     read once, 16 bytes a lane, a CTA per row and chunk of keys; scores are capped (cap > 0), seen inside the window
     (window > 0), softmaxed with the sink (sink; sink_values [H] float32: learnt ones) and, with talk [H, H] float32,
     the heads' weights mixed after the softmax; values_in_keys: the values are the first dv features of the keys.
     q_rows [T, >= H d], out [T, H dv]; max_keys bounds the keys a row sees; scratch float32 of at least
-    `talk_attention_rows_floats`.  Sums are float and their order depends on the row alone."""
+    `talk_attention_rows_floats`.  keep_first (with a window): the sequence's first positions that stay seen behind the
+    window; max_keys counts them too.  Sums are float and their order depends on the row alone."""
     T = q_rows.shape[0]
     _t(q_rows, "q_rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
@@ -911,7 +912,7 @@ def talk_attention_rows(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_t
         _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None, out.data_ptr(), T, H, G, d, dv,
         float(scale), 1 if sink else 0, int(max_keys), int(window), float(cap),
         _t(sink_values, "sink_values", torch.float32, (H,)) if sink_values is not None else None,
-        1 if values_in_keys else 0, _t(scratch, "scratch", torch.float32), scratch.numel(), _stream()), kernels=4)
+        1 if values_in_keys else 0, _t(scratch, "scratch", torch.float32), scratch.numel(), int(keep_first), _stream()), kernels=4)
     return out
 
 

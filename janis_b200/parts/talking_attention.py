@@ -152,6 +152,20 @@ class TalkingHeadsAttention(Mixer):
         att = ws.buf("tattn.ctx", (T, H * dv), rt.dtype)
         decode = ctx.mode == "decode"
         max_keys, n_chunks, scratch = 0, 1, None
+        rows_floats = 0
+        if (decode and rt.dtype == torch.bfloat16 and not self.block and not self.sink and self.talk is None and inv_v is None
+                and hasattr(ops, "talk_attention_rows_floats")):
+            # a decode step in the serving dtype with nothing the kernels that take single rows leave out: keys and
+            # values read once, 16 bytes a lane
+            max_keys = min(ctx.len_bound, self.window + self.keep_first) if self.window else ctx.len_bound
+            rows_floats = ops.talk_attention_rows_floats(rt.dtype, T, H, G, d, dv, max_keys)
+        if rows_floats:
+            ops.talk_attention_rows(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, None, att, H, G, d, dv,
+                                    self.scale, ws.buf("tattn.rows_scratch", (rows_floats,), torch.float32), max_keys,
+                                    window=self.window, **({"keep_first": self.keep_first} if self.keep_first else {}))
+            if "g" in self.names:
+                ops.sigmoid_gate(att, rows, g_off, per=dv if self.gate == "head" else 1)
+            return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))
         if decode:
             # a decode row's keys over several CTAs when the rows alone would leave most of the GPU idle: about a
             # CTA an SM in all, none with fewer than 128 keys (the bound on the lengths is the host's)

@@ -402,11 +402,11 @@ def talk_attention_rows_floats(dtype, T, H, G, d, dv, max_keys):
 
 
 def talk_attention_rows(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, out, H, G, d, dv, scale, scratch,
-                        max_keys, sink=False, window=0, cap=0.0, sink_values=None, values_in_keys=False):
+                        max_keys, sink=False, window=0, cap=0.0, sink_values=None, values_in_keys=False, keep_first=0):
     """The same mathematics as `talk_attention` with the heads mixed after the softmax."""
     return talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, None, out, H, G, d, dv, scale,
                           0, sink, window=window, cap=cap, sink_values=sink_values, mix_after=True,
-                          values_in_keys=values_in_keys)
+                          values_in_keys=values_in_keys, keep_first=keep_first)
 
 
 def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, H,

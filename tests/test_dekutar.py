@@ -83,11 +83,11 @@ def _model(vocab, width, streams, eps, emb, logit, layers):
 
 
 # two copies; a window that is no whole page with three kept positions; part of the head turned; identity entries
-DEK_A = _model(200, 64, 2, 1e-6, 8.0, 2.0, [
+DEK_A = _model(200, 64, 2, 1e-6, 8.0, 1.25, [
     ("latent_attention", _lat(4, 16, 8, 16, 24, 40, 0.2, base=1000.0), _moe(6, 2, 3, 24, shared=40)),
     ("attention", _att(4, 1, 16, 0.25, rot=8, base=100.0, window=24, keep=3), _moe(6, 2, 3, 24, shared=40)),
-    ("mlstm", _mem(2, 16, 24, 15.0), _moe(6, 2, 3, 24, shared=40)),
-    ("latent_attention", _lat(2, 8, 16, 24, 32, 16, 0.2, base=50000.0), None)])
+    ("mlstm", _mem(2, 16, 24, 11.0), _moe(6, 2, 3, 24, shared=40)),
+    ("latent_attention", _lat(2, 8, 16, 24, 32, 16, 0.2, base=20000.0), None)])
 
 # three copies; the matrix memory first; as many key/value heads as heads; a window without kept positions and no
 # window; the whole head turned; no identity entries, no shared expert, one expert chosen
@@ -98,10 +98,10 @@ DEK_B = _model(333, 96, 3, 1e-5, 1.0, 0.5, [
     ("attention", _att(2, 1, 32, 0.2, rot=2), _moe(4, 0, 1, 32))])
 
 # the plain residual sum; sizes a tensor-core kernel takes; a window of two whole pages with eight kept positions
-DEK_C = _model(512, 128, 0, 1e-6, 12.0, 1.0, [
-    ("attention", _att(8, 2, 64, 0.12, rot=32, base=300000.0, window=128, keep=8), _moe(8, 4, 4, 64, shared=96)),
-    ("latent_attention", _lat(8, 32, 32, 32, 96, 64, 0.12, base=300000.0), _moe(8, 4, 4, 64, shared=96)),
-    ("mlstm", _mem(4, 64, 64, 15.0), None),
+DEK_C = _model(640, 128, 0, 1e-6, 10.0, 1.0, [
+    ("attention", _att(8, 2, 64, 0.12, rot=32, base=300000.0, window=128, keep=8), _moe(8, 4, 4, 48, shared=80)),
+    ("latent_attention", _lat(8, 32, 32, 32, 80, 64, 0.12, base=300000.0), _moe(8, 4, 4, 48, shared=80)),
+    ("mlstm", _mem(4, 64, 64, 20.0), None),
     ("attention", _att(16, 16, 16, 0.25, rot=16, window=64, keep=1), _moe(16, 0, 2, 32))])
 
 # one copy behind its maps; sizes that are multiples of little; a window of five with one kept position and a window of
@@ -214,7 +214,7 @@ def test_configuration_reads_back_and_guards():
     cfg = DekutarConfig.from_dict(DEK_A)
     assert DekutarConfig.from_dict(cfg.to_dict()) == cfg
     assert resolve(DEK_A).name == "Dekutar"
-    assert cfg.streams == 2 and cfg.logit_scale == 2.0 and cfg.embedding_scale == 8.0
+    assert cfg.streams == 2 and cfg.logit_scale == 1.25 and cfg.embedding_scale == 8.0
     assert cfg.layers[1].mixer.window == 24 and cfg.layers[1].mixer.keep_first == 3 and cfg.layers[1].mixer.rot_dims == 8
     assert cfg.layers[3].mlp is None and cfg.layers[0].mlp.identity == 2 and cfg.layers[0].mlp.shared_ff == 40
     assert DekutarConfig.from_dict(DEK_C).streams == 0
@@ -416,6 +416,15 @@ def test_window_with_kept_first_positions_against_its_statement(dtype, H, G, d, 
         finally:
             ops.talk_attention_set_kernel(1)
         _close(got, want, dtype, (which, one_row, chunks))
+    # the kernels that take single rows (decode steps), with bounds that cut a row's keys into one chunk and several
+    for bound in (min(window + keep, 300), 5000):
+        n = ops.talk_attention_rows_floats(dtype, T, H, G, d, d, bound)
+        assert (n > 0) == (d % (4 if dtype == torch.float32 else 8) == 0)
+        if n:
+            got = torch.full((T, H * d), float("nan"), dtype=dtype, device="cuda")
+            ops.talk_attention_rows(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), None, got, H, G, d, d,
+                                    0.4, torch.full((n,), float("nan"), device="cuda"), bound, window=window, keep_first=keep)
+            _close(got, want, dtype, ("rows", bound))
 
 
 @GPU
