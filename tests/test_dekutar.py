@@ -785,3 +785,40 @@ def test_trace_replay_and_command_line_as_a_user_runs_them(dek_dirs, plain, tmp_
     for _ in range(4):
         seq.append(int(plain(key, steep, seq)[-1].argmax()))
     assert ",".join(map(str, seq[len(reqs[1]):])) in p.stdout.replace(" ", ""), p.stdout
+
+
+def test_the_comparison_model_of_the_benchmark_builds_at_every_size():
+    from janis_b200 import DekutarConfig, build_model
+    from janis_b200.benchmark import dekutar_like, load_config
+    for name in ("gemma2-2b", "gemma2-9b", "gemma2-27b"):
+        gemma = load_config(name)
+        raw = dekutar_like(gemma, 4)
+        cfg = DekutarConfig.from_dict(raw)
+        assert [l.type for l in cfg.layers] == ["latent_attention", "attention", "mlstm", "attention"] and cfg.streams == 2
+        _, _, model = build_model(raw)
+        assert model.stream_width == 2 * gemma["hidden_size"] and model.vocab == gemma["vocab_size"]
+        assert all(n.shape for n in model.tensor_specs().values() if n.shape != ())
+
+
+# three layers at sizes that reach the launch shapes, vector loads and library products the small models do not
+DEK_WIDE = _model(2048, 1024, 2, 1e-6, 6.0, 0.75, [
+    ("attention", _att(8, 2, 128, 0.09, rot=64, base=100000.0, window=256, keep=4), _moe(8, 2, 2, 512, shared=512)),
+    ("mlstm", _mem(8, 128, 128, 14.0), _moe(8, 2, 2, 512, shared=512)),
+    ("latent_attention", _lat(8, 64, 32, 64, 128, 384, 0.1, base=100000.0), _moe(8, 2, 2, 512, shared=512))])
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_three_layers_at_the_sizes_of_a_larger_model(tmp_path_factory, dtype):
+    from tests.plain import dekutar_plain as P
+    d = str(tmp_path_factory.mktemp("dekutar_wide"))
+    write_dekutar(d, DEK_WIDE, 91, steep_router=dtype == "bfloat16", gain=1.0, qk_gain=2.0, router_gain=4.0)
+    cfg, w = P.load_folder(d)
+    eng = make_engine(d, dtype, "cuda", max_tokens=4096)
+    try:
+        reqs = _requests(DEK_WIDE["vocab"], [560, 300, 40], 95)
+        got = run_requests(eng, reqs, [520, 270, 3])
+        for r, g_ in zip(reqs, got):
+            assert_logits(g_, P.forward(cfg, w, r), dtype, f"wide {len(r)}")
+    finally:
+        eng.close()
