@@ -103,7 +103,9 @@ hc_read_norm_kernel(const float* __restrict__ h, const int* __restrict__ rows, c
     for (int c = tid; c < W; c += nt) o[c] = from_float<T>(hc_u[c] * inv * w[c]);
 }
 
-template <typename T, typename TO>
+// (SMAX: a compile-time bound on the copies, 2, 4 or 8: the loops over the copies are unrolled to it, and what a thread
+// keeps in registers follows)
+template <typename T, typename TO, int SMAX>
 __global__ void __launch_bounds__(256)
 hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* __restrict__ M, const float* __restrict__ b,
                  const float* __restrict__ a_next, const float* __restrict__ w_next, float eps_next,
@@ -127,19 +129,19 @@ hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* 
     const bool vec = (W & 3) == 0 && (((uintptr_t)h | (uintptr_t)res | (uintptr_t)out | (uintptr_t)w_next) & 15) == 0;
     for (int c = tid * 4; vec && c < W; c += nt * 4) {
         // four elements a thread: every copy 16 bytes a load and a store; the sums per element in the order of the loop below
-        float y[4], fresh[HC_MAX][4];
+        float y[4], fresh[SMAX][4];
         load4(rr + c, y);
 #pragma unroll
-        for (int k = 0; k < HC_MAX; ++k)
+        for (int k = 0; k < SMAX; ++k)
 #pragma unroll
             for (int e = 0; e < 4; ++e) fresh[k][e] = 0.f;
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s)
+        for (int s = 0; s < SMAX; ++s)
             if (s < S) {
                 float old[4];
                 load4(x + (size_t)s * W + c, old);
 #pragma unroll
-                for (int k = 0; k < HC_MAX; ++k)
+                for (int k = 0; k < SMAX; ++k)
                     if (k < S) {
                         const float m = m_s[s * S + k];
 #pragma unroll
@@ -148,7 +150,7 @@ hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* 
             }
         float u[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int k = 0; k < HC_MAX; ++k)
+        for (int k = 0; k < SMAX; ++k)
             if (k < S) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -164,17 +166,17 @@ hc_update_kernel(float* __restrict__ h, const T* __restrict__ res, const float* 
         }
     }
     for (int c = tid; !vec && c < W; c += nt) {
-        float old[HC_MAX];
+        float old[SMAX];
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s) old[s] = s < S ? x[(size_t)s * W + c] : 0.f;
+        for (int s = 0; s < SMAX; ++s) old[s] = s < S ? x[(size_t)s * W + c] : 0.f;
         const float y = to_float(rr[c]);
         float u = 0.f;
 #pragma unroll
-        for (int k = 0; k < HC_MAX; ++k)
+        for (int k = 0; k < SMAX; ++k)
             if (k < S) {
                 float v = 0.f;
 #pragma unroll
-                for (int s = 0; s < HC_MAX; ++s)
+                for (int s = 0; s < SMAX; ++s)
                     if (s < S) v = fmaf(m_s[s * S + k], old[s], v);
                 v = fmaf(b_s[k], y, v);
                 x[(size_t)k * W + c] = v;
@@ -247,11 +249,19 @@ JANIS_EXPORT int janis_hc_update(float* h, const void* res, int dtype, const flo
     if ((a_next == nullptr) != (w_next == nullptr) || (w_next != nullptr && out == nullptr))
         return fail("hc_update: the next sublayer's read needs its vector, its norm's weight and a place for the result");
     const dim3 grid(R), block(W >= 1024 ? 256 : 128);
-    if (dtype == JANIS_F32)
-        return launch_kernel("hc_update", hc_update_kernel<float, float>, grid, block, bytes, stream, 1, h, (const float*)res, M, b,
-                             a_next, w_next, eps_next, (float*)out, S, W);
-    if (dtype == JANIS_BF16)
-        return launch_kernel("hc_update", hc_update_kernel<bf16, bf16>, grid, block, bytes, stream, 1, h, (const bf16*)res, M, b,
-                             a_next, w_next, eps_next, (bf16*)out, S, W);
+#define JANIS_HC_UPDATE(TT, SMAX)                                                                                      \
+    return launch_kernel("hc_update", hc_update_kernel<TT, TT, SMAX>, grid, block, bytes, stream, 1, h, (const TT*)res, M, b, \
+                         a_next, w_next, eps_next, (TT*)out, S, W);
+    if (dtype == JANIS_F32) {
+        if (S <= 2) JANIS_HC_UPDATE(float, 2)
+        if (S <= 4) JANIS_HC_UPDATE(float, 4)
+        JANIS_HC_UPDATE(float, 8)
+    }
+    if (dtype == JANIS_BF16) {
+        if (S <= 2) JANIS_HC_UPDATE(bf16, 2)
+        if (S <= 4) JANIS_HC_UPDATE(bf16, 4)
+        JANIS_HC_UPDATE(bf16, 8)
+    }
+#undef JANIS_HC_UPDATE
     return fail("hc_update: unknown dtype %d", dtype);
 }
