@@ -73,10 +73,15 @@ def build_dekutar(cfg: DekutarConfig) -> DecoderModel:
         return parts.make("norm", "rms_norm", width=W, eps=eps, weight_name=name, offset=1.0)
 
     blocks = []
+    # what a folder may carry without its model using it: the second sublayer's norm and maps of a layer that has no
+    # feed-forward, and maps of copies in a model with one stream and the plain sum
+    unused = [] if S else ["l*.hc1.*", "l*.hc2.*"]
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}"
         mixer = _MIXERS[layer.type](W, f"{p}.mix", layer.mixer, eps)
         ff = _experts(W, f"{p}.mlp", layer.mlp) if layer.mlp is not None else None
+        if ff is None:
+            unused += [f"{p}.norm2", f"{p}.hc2.*"]
         if S:
             names = {"mix1": f"{p}.hc1.mix", "out1": f"{p}.hc1.out"}
             if ff is not None:
@@ -96,6 +101,7 @@ def build_dekutar(cfg: DekutarConfig) -> DecoderModel:
         head=parts.make("head", "capped_linear", vocab=cfg.vocab, hidden=W, table_name="head", softcap=0.0,
                         scale=cfg.logit_scale, init_std=W ** -0.5),
         schedule=[LayerCall(i, i) for i in range(len(blocks))],
+        ignorable_tensors=unused,
         max_context=1 << 20)
 
 

@@ -230,6 +230,7 @@ def test_configuration_reads_back_and_guards():
     assert set(needs[0]) == {"kv"} and needs[0]["kv"].n_kv_heads == 1 and needs[0]["kv"].head_dim == 32
     assert needs[1]["kv"].n_kv_heads == 1 and needs[1]["kv"].value_dim == 16
     assert set(needs[2]) == {"memory", "normaliser", "maximum"} and needs[2]["memory"].shape == (2, 24, 16)
+    assert "l3.norm2" in model.ignorable_tensors and "l3.hc2.*" in model.ignorable_tensors and "l0.norm2" not in model.ignorable_tensors
     _, _, plain_model = build_model(DEK_C)
     assert "l0.hc1.in" not in plain_model.tensor_specs() and plain_model.stream_width == 128 and model.stream_width == 128
     bad_layers = [
