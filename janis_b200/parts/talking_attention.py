@@ -121,6 +121,10 @@ class TalkingHeadsAttention(Mixer):
             store.drop(n["q"], n["g"])
         else:
             self.w_qkv = store.get(n["q"], rt.dtype).contiguous()
+        if self.w_qkv.shape[0] % 8:
+            # rows of the step in whole 16-byte pieces (a gate per head may leave any number of columns): zero rows behind the last
+            pad = torch.zeros(8 - self.w_qkv.shape[0] % 8, self.w_qkv.shape[1], dtype=self.w_qkv.dtype, device=self.w_qkv.device)
+            self.w_qkv = torch.cat([self.w_qkv, pad], dim=0).contiguous()
         self.w_o = store.get(n["o"], rt.dtype).contiguous()
         self.talk = store.get(n["talk"]).to(torch.float32).contiguous() if "talk" in n else None
 
@@ -132,8 +136,7 @@ class TalkingHeadsAttention(Mixer):
         T, H, G, d, dv = ctx.n_tok, self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
         kv_cols = (G * d if self.values_from_keys else G * (d + dv)) if self.own_kv else 0
         g_off = H * d + kv_cols                                        # where the gate's logits start in a row
-        width = g_off + (0 if "g" not in self.names else (H * dv if self.gate == "element" else H))
-        rows = ws.buf("tattn.rows", (T, width), rt.dtype)
+        rows = ws.buf("tattn.rows", (T, self.w_qkv.shape[0]), rt.dtype)      # (the product's columns: the gate's, and padding, last)
         rt.linear(x, self.w_qkv, rows)
         inv_v = self.value_position.inv_freq if self.value_position is not None else None
         neighbours = self.position.pairs == "neighbours" and self.position.rot > 0
