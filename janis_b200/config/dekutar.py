@@ -10,8 +10,9 @@ without the key a layer is the plain pre-norm one with a single stream.
 
 A "latent_attention" mixer gives heads, dim (the part of a query/key head that is not rotated), rot_dim (the
 rotated part), vdim, kv_rank (the compressed key/value row), q_rank (the compressed query row), scale, rot.base and
-rot.dims.  An "attention" mixer gives heads, kv_heads, dim (queries and keys; the values are the keys as projected,
-so vdim equals dim), scale, rot.base, rot.dims (the first features of a head that turn; absent or 0: none),
+rot.dims (the first features of the rotated part that turn: all of them, as a rule).  An "attention" mixer gives
+heads, kv_heads, dim (queries and keys; the values are the keys as projected, so vdim equals dim), scale, rot.base,
+rot.dims (the first features of a head that turn; absent or 0: none),
 mask.size (the sliding window; absent or 0: every earlier key is seen) and mask.keep_first (the sequence's first
 positions that stay seen behind the window).  An "mlstm" mixer gives heads, dim (queries and keys), vdim and
 gate_cap.  A feed-forward gives expert.ff, router.experts (the experts that have tensors), router.identity (further
@@ -118,8 +119,6 @@ def _latent(r: ConfigReader) -> QueryLatentAttentionSpec:
     if dim + rot_dim < 1:
         raise ConfigError(f"{r.where}: a query head needs at least one feature")
     base, dims = _rot(r, rot_dim, required=rot_dim > 0)
-    if rot_dim and dims != rot_dim:
-        raise ConfigError(f"{r.where}: the rotated part turns as a whole: rot.dims ({dims}) must equal rot_dim ({rot_dim})")
     return QueryLatentAttentionSpec(heads=r.integer("heads", minimum=1), dim=dim, rot_dim=rot_dim,
                                     vdim=r.integer("vdim", minimum=1), kv_rank=r.integer("kv_rank", minimum=1),
                                     q_rank=r.integer("q_rank", minimum=1),

@@ -116,7 +116,7 @@ DEK_D = _model(301, 72, 1, 1e-4, 3.0, 1.5, [
 # each mixer alone, without a feed-forward; a width that is no multiple of 8
 DEK_E = _model(150, 48, 2, 1e-6, 1.0, 1.0, [("mlstm", _mem(3, 16, 16, 10.0), None)])
 DEK_F = _model(97, 36, 4, 1e-5, 2.0, 3.0, [("attention", _att(2, 1, 12, 0.3, rot=12, window=9, keep=2), None),
-                                          ("latent_attention", _lat(2, 4, 4, 6, 12, 6, 0.3), _moe(2, 1, 2, 18))])
+                                          ("latent_attention", {**_lat(2, 4, 4, 6, 12, 6, 0.3), "rot": {"base": 10000.0, "dims": 2}}, _moe(2, 1, 2, 18))])
 
 DEK = {"A": DEK_A, "B": DEK_B, "C": DEK_C, "D": DEK_D, "E": DEK_E, "F": DEK_F}
 
@@ -462,8 +462,9 @@ def test_turn_norm_store_kernel_against_its_statement(dtype, H, G, d, rot, halve
 
 @GPU
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,dr,R", [(4, 16, 8, 24), (3, 12, 6, 10), (8, 32, 32, 96), (1, 6, 2, 7), (2, 0, 4, 12)])
-def test_compressed_row_kernel_turns_halves_and_takes_queries_of_their_own(dtype, H, d, dr, R):
+@pytest.mark.parametrize("H,d,dr,R,rot", [(4, 16, 8, 24, 8), (3, 12, 6, 10, 6), (8, 32, 32, 96, 32), (1, 6, 2, 7, 2), (2, 0, 4, 12, 4), (4, 16, 8, 24, 4),
+                                          (2, 8, 16, 20, 6)])
+def test_compressed_row_kernel_turns_halves_and_takes_queries_of_their_own(dtype, H, d, dr, R, rot):
     from janis_b200.kernels import ops
     from tests import kernel_refs as Rf
     g = torch.Generator().manual_seed(2)
@@ -479,11 +480,11 @@ def test_compressed_row_kernel_turns_halves_and_takes_queries_of_their_own(dtype
     kp = torch.randn(4 * per_seq, 1, ops.PAGE, R + dr, generator=g).to(dtype)
     qfull = torch.randn(T, H * (R + dr), generator=g).to(dtype)
     want_k, want_q = kp.clone(), qfull.clone()
-    Rf.latent_rotate_store(rows, 0, H, d, dr, R, wc, 1e-5, inv, 1.0, tok_pos, tok_seq, seq_slot, want_q, want_k, table, rot=dr,
+    Rf.latent_rotate_store(rows, 0, H, d, dr, R, wc, 1e-5, inv, 1.0, tok_pos, tok_seq, seq_slot, want_q, want_k, table, rot=rot,
                            q_rows=q_rows, halves=True)
     got_k, got_q = kp.cuda(), qfull.cuda()
     ops.latent_rotate_store(rows.cuda(), 0, H, d, dr, R, wc.cuda(), 1e-5, inv.cuda(), 1.0, tok_pos.cuda(), tok_seq.cuda(),
-                            seq_slot.cuda(), got_q, got_k, table.cuda(), rot=dr, q_rows=q_rows.cuda(), halves=True)
+                            seq_slot.cuda(), got_q, got_k, table.cuda(), rot=rot, q_rows=q_rows.cuda(), halves=True)
     _close(got_q, want_q, dtype, "queries")
     _close(got_k, want_k, dtype, "keys")
 
